@@ -1,0 +1,49 @@
+// Shared helpers for the sm_100a kernels: error reporting for the C ABI, bf16 bit tricks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ferrite_b200.h"
+
+namespace fb {
+
+// Last error text of the calling thread; every extern "C" entry point returns 0 or a negative
+// fb_status and leaves the reason here (fb_last_error()).
+void set_error(const char* fmt, ...);
+int launch_status(const char* what);  // cudaGetLastError() -> FB_OK / FB_ERR_LAUNCH with the message kept
+
+#define FB_REQUIRE(cond, ...)            \
+  do {                                   \
+    if (!(cond)) {                       \
+      fb::set_error(__VA_ARGS__);        \
+      return FB_ERR_ARG;                 \
+    }                                    \
+  } while (0)
+
+__host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+// float -> bf16 bits, round to nearest even (what an upload of Python floats does: ferrite/tensor.py:56)
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float f) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace fb

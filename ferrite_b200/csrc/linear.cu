@@ -1,0 +1,27 @@
+// fb_linear: argument checks (what ferrite's Tensor.matmul asserts, ferrite/tensor.py:443-485) and the
+// choice between the GEMV and the tensor-core kernels.
+#include "linear.cuh"
+
+extern "C" size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N) { return fb::linear_tcgen05_workspace(M, K, N); }
+
+extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out,
+                         int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,
+                         int64_t ldr, void* workspace, size_t workspace_bytes, void* stream) {
+  FB_REQUIRE(fmt == FB_BFP8 || fmt == FB_BFP4, "fb_linear: W is bfp8 or bfp4 (dtype %d given)", fmt);
+  FB_REQUIRE(x && W && out, "fb_linear: null pointer");
+  FB_REQUIRE(M >= 1 && K >= 4 && K % 4 == 0 && N >= 16 && N % 16 == 0, "fb_linear: [%lld, %lld] @ [%lld, %lld]: K a multiple of 4, N of 16",
+             (long long)M, (long long)K, (long long)K, (long long)N);
+  FB_REQUIRE(out_dtype == FB_BF16 || out_dtype == FB_FP32, "fb_linear: out is bf16 or fp32");
+  FB_REQUIRE(epilogue >= FB_EPI_NONE && epilogue <= FB_EPI_RESIDUAL, "fb_linear: unknown epilogue %d", epilogue);
+  FB_REQUIRE(epilogue != FB_EPI_SWIGLU || N % 32 == 0, "fb_linear: SwiGLU pairs column j with j + N/2: N a multiple of 32");
+  FB_REQUIRE(epilogue != FB_EPI_RESIDUAL || residual, "fb_linear: the residual epilogue needs a residual");
+  const int64_t out_cols = epilogue == FB_EPI_SWIGLU ? N / 2 : N;
+  FB_REQUIRE(ldx >= K && ldx % 4 == 0 && ldo >= out_cols && (epilogue != FB_EPI_RESIDUAL || ldr >= N), "fb_linear: row strides too small or unaligned");
+  FB_REQUIRE((uintptr_t)x % 8 == 0 && (uintptr_t)W % 16 == 0 && (uintptr_t)out % 4 == 0 && (!norm_w || (uintptr_t)norm_w % 8 == 0),
+             "fb_linear: misaligned pointer");
+  FB_REQUIRE(fmt == FB_BFP8 || (K * N) % 32 == 0, "fb_linear: a bfp4 W has rows x cols a multiple of 32");
+  fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, norm_w, eps, epilogue, residual, ldr, workspace, workspace_bytes};
+  auto s = (cudaStream_t)stream;
+  if (M > 4 && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);
+  return fb::linear_gemv(a, s);
+}

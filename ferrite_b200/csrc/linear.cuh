@@ -1,0 +1,30 @@
+// Arguments of fb_linear as the kernels see them, and the implementations it dispatches to.
+#pragma once
+#include "common.cuh"
+
+namespace fb {
+
+struct LinearArgs {
+  int fmt;               // FB_BFP8 | FB_BFP4 | FB_BF16
+  const void* x;         // [M, K] bf16, rows ldx apart
+  int64_t M, K, ldx;
+  const void* W;         // packed [K, N]
+  int64_t N;
+  void* out;             // [M, N] or [M, N/2] (SwiGLU), rows ldo apart
+  int out_dtype;         // FB_BF16 | FB_FP32
+  int64_t ldo;
+  const void* norm_w;    // [K] bf16 or null: RMSNorm prologue
+  float eps;
+  int epilogue;          // fb_epilogue
+  const void* residual;  // [M, N] bf16, rows ldr apart (FB_EPI_RESIDUAL)
+  int64_t ldr;
+  void* workspace;
+  size_t workspace_bytes;
+};
+
+int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: M <= 4 per pass, CUDA cores
+int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores
+bool linear_tcgen05_supports(const LinearArgs& a);
+size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N);
+
+}  // namespace fb

@@ -1,0 +1,37 @@
+"""The C-ABI library loads and exports every symbol include/ferrite_b200.h declares (no GPU needed)."""
+import os
+import re
+
+from conftest import ROOT
+from ferrite_b200 import _lib
+
+
+def declared():
+    text = open(os.path.join(ROOT, "include", "ferrite_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.lib()
+    names = declared()
+    assert "fb_linear" in names and "fb_quantize" in names
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signatures without a declaration"
+
+
+def test_host_side_calls():
+    lib = _lib.lib()
+    assert lib.fb_version() >= 1
+    assert lib.fb_packed_bytes(_lib.BFP8, 32, 32) == 1088 and lib.fb_packed_bytes(_lib.BFP4, 32, 32) == 576  # ferrite/compiler.py:19-20
+    assert lib.fb_packed_bytes(_lib.BFP8, 32, 40) == 0, "columns come in runs of 16"
+
+
+def test_bad_arguments_are_refused_without_a_gpu():
+    lib = _lib.lib()
+    rc = lib.fb_quantize(_lib.BF16, None, 1, 32, 32, None, None)
+    assert rc == -1 and b"block float" in lib.fb_last_error()
+    rc = lib.fb_linear(_lib.BFP8, 16, 1, 30, 32, 16, 32, 16, _lib.BF16, 32, None, 1e-5, 0, None, 0, None, 0, None)
+    assert rc == -1 and b"multiple of 4" in lib.fb_last_error()

@@ -1,0 +1,83 @@
+"""fb_linear: block-float weight matmul with fused RMSNorm prologue and SwiGLU / residual epilogue against
+the numpy oracle (the reference's numpy branch: exact products, models/llama.py:33, 82-85, 266-275)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import to_bf16_tensor, to_numpy
+from ferrite_b200 import ops
+from oracle import bfp, llama
+
+pytestmark = pytest.mark.gpu
+
+
+def case(rng, M, K, N, fmt, cuda, sigma=0.02):
+    x = bfp.bf16_round(rng.normal(0, 1, (M, K)).astype(np.float32))
+    w = bfp.bf16_round(rng.normal(0, sigma, (K, N)).astype(np.float32))
+    packed = ops.quantize(to_bf16_tensor(w, cuda), fmt)
+    return x, bfp.bfp(w, fmt), to_bf16_tensor(x, cuda), packed
+
+
+def rel_err(got, want):
+    return np.abs(got - want).max() / np.abs(want).max()
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("M,K,N", [(1, 768, 2304), (1, 4096, 4096), (3, 576, 960), (4, 1536, 576), (7, 256, 64), (1, 64, 16)])
+def test_plain_matmul(cuda, fmt, M, K, N):
+    rng = np.random.default_rng(M * 1000 + K + N)
+    x, wq, tx, packed = case(rng, M, K, N, fmt, cuda)
+    want = x.astype(np.float64) @ wq
+    got32 = to_numpy(ops.linear(tx, packed, out_dtype="fp32"))
+    assert rel_err(got32, want) < 2e-5, "fp32 accumulation of exact products"
+    got16 = to_numpy(ops.linear(tx, packed))
+    assert np.array_equal(got16, to_numpy(torch.from_numpy(got32.astype(np.float32)).bfloat16())), "bf16 output is the fp32 one rounded once"
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("M", [1, 2, 4, 6])
+def test_rmsnorm_prologue_and_swiglu_epilogue(cuda, fmt, M):
+    rng = np.random.default_rng(40 + M)
+    K, N = 1024, 2048
+    x, wq, tx, packed = case(rng, M, K, N, fmt, cuda)
+    g = bfp.bf16_round(rng.normal(1, 0.1, (1, K)).astype(np.float32))
+    h = llama.rms(x.astype(np.float64), g, 1e-5)
+    gu = h @ wq
+    want = llama.glu(gu[:, :N // 2], gu[:, N // 2:])
+    got = to_numpy(ops.linear(tx, packed, norm_w=to_bf16_tensor(g, cuda), eps=1e-5, epilogue="swiglu"))
+    assert got.shape == (M, N // 2)
+    assert rel_err(got, want) < 6e-3, "one bf16 rounding of the output"
+    plain = to_numpy(ops.linear(tx, packed, norm_w=to_bf16_tensor(g, cuda), eps=1e-5, out_dtype="fp32"))
+    assert rel_err(plain, gu) < 2e-5
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_residual_epilogue(cuda, fmt):
+    rng = np.random.default_rng(7)
+    M, K, N = 3, 1536, 576
+    x, wq, tx, packed = case(rng, M, K, N, fmt, cuda)
+    r = bfp.bf16_round(rng.normal(0, 1, (M, N)).astype(np.float32))
+    want = r + x.astype(np.float64) @ wq
+    got = to_numpy(ops.linear(tx, packed, epilogue="residual", residual=to_bf16_tensor(r, cuda)))
+    assert rel_err(got, want) < 5e-3
+    got32 = to_numpy(ops.linear(tx, packed, epilogue="residual", residual=to_bf16_tensor(r, cuda), out_dtype="fp32"))
+    assert rel_err(got32, want) < 2e-5
+
+
+def test_bfp_matmul_equals_the_matmul_by_its_values(cuda):
+    # the reference's claim for a block-float B (test/test_sim.py:373-377): the same result as the matmul by the
+    # values it holds; here: quantising the dequantised weight again changes no output bit
+    rng = np.random.default_rng(5)
+    for fmt in ("bfp8", "bfp4"):
+        x, wq, tx, packed = case(rng, 2, 768, 256, fmt, cuda)
+        again = ops.quantize(ops.dequantize(packed)[0].contiguous(), fmt)
+        assert torch.equal(ops.linear(tx, packed, out_dtype="fp32"), ops.linear(tx, again, out_dtype="fp32"))
+
+
+def test_misuse_is_refused(cuda):
+    x = torch.zeros(1, 64, dtype=torch.bfloat16, device=cuda)
+    w = ops.quantize(torch.zeros(64, 48, dtype=torch.bfloat16, device=cuda), "bfp8")
+    with pytest.raises(AssertionError):
+        ops.linear(x, w, epilogue="swiglu")  # 48 columns do not pair up in runs of 16
+    with pytest.raises(AssertionError):
+        ops.linear(x, w, epilogue="residual")  # no residual given

@@ -1,0 +1,111 @@
+"""The CPU oracle against the fixtures generated from the unmodified reference (tests/golden/make_golden.py)."""
+import hashlib
+
+import numpy as np
+import pytest
+
+from conftest import golden
+from oracle import bfp, llama
+
+
+def test_bf16_rounding_is_nearest_even():
+    a = np.array([1.0, 1 + 2.0 ** -8, 1 + 3 * 2.0 ** -8, -(1 + 2.0 ** -8), 1 + 2.0 ** -8 + 2.0 ** -20], np.float32)
+    assert bfp.bf16_bits(a).tolist() == [0x3F80, 0x3F80, 0x3F82, 0xBF80, 0x3F81]
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_bfp_matches_reference_vectors(fmt):
+    g = golden("bfp.npz")
+    for name in ("spread", "edge", "wide", "weights"):
+        x = bfp.bf16_floats(g[f"{name}.bits"])
+        assert np.array_equal(bfp.bfp(x, fmt), g[f"{name}.{fmt}"]), name
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_fields_properties(fmt):
+    x = bfp.bf16_floats(golden("bfp.npz")["edge.bits"])
+    top, sign, mag = bfp.fields(x, fmt)
+    assert mag.max() <= (127 if fmt == "bfp8" else 7)
+    assert not sign[mag == 0].any(), "a zero is stored without a sign"
+    y = bfp.bfp(bfp.bf16_floats(golden("bfp.npz")["spread.bits"]), fmt)  # (normal numbers: a run of bf16 denormals halves, models/gpt2.py:26)
+    assert np.array_equal(bfp.bfp(y, fmt), y), "quantising twice changes nothing"
+
+
+def test_topk_matches_reference_vectors():
+    g = golden("topk.npz")
+    for i in range(len(g.files) // 3):
+        x = bfp.bf16_floats(g[f"{i}.bits"])
+        vals, ids = llama.topk(x, int(g[f"{i}.k"]))
+        assert np.array_equal(ids, g[f"{i}.ids"])
+
+
+def test_touched_known_answer():
+    # the reference's own expectation (test/test_sim.py:1528-1529): expert 5, weighted 0, is not listed
+    ids = np.array([[0, 3], [5, 3], [7, 1]])
+    w = np.array([[0.5, 0.5], [0, 0], [0.25, 0.75]], np.float32)
+    experts, weights = llama.touched(ids, w, 8)
+    assert experts[:, 0].tolist() == [0, 1, 3, 7, 8, 8]
+    assert weights[2, :, 0].tolist() == [0.5, 0, 0] and weights[3, :, 0].tolist() == [0, 0, 0.25]
+
+
+def test_moe_matches_reference_vectors():
+    g = golden("moe.npz")
+    w = {k: bfp.bf16_floats(g[k]) for k in ("router", "experts.gate_up", "experts.down")}
+    c = llama.model(dim=64, k=4)
+    for n in (1, 3, 8, 40):
+        h, live = bfp.bf16_floats(g[f"h{n}"]), np.float32(np.arange(n) != 1).reshape(n, 1)
+        assert np.allclose(llama.moe(h, w, c, live=live), g[f"y{n}"], rtol=1e-12, atol=1e-12)
+
+
+def _checksum(w):
+    h = hashlib.sha256()
+    for k in sorted(w):
+        h.update(k.encode())
+        h.update(np.ascontiguousarray(w[k], np.float32).tobytes())
+    return h.hexdigest()
+
+
+MODELS = {
+    "dense_bfp8": (dict(dim=256, heads=4, kv=2, layers=2, eps=1e-5, theta=10000.0, vocab=512, ffn=512, places=64), "bfp8", None),
+    "dense_bfp4": (dict(dim=256, heads=4, kv=2, layers=2, eps=1e-5, theta=10000.0, vocab=512, ffn=512, places=64), "bfp4", None),
+    "smol_shape": (dict(dim=576, heads=9, kv=3, layers=2, eps=1e-5, theta=10000.0, vocab=1024, ffn=1536, places=64), "bfp8", None),
+    "slots4": (dict(dim=256, heads=4, kv=2, layers=2, eps=1e-5, theta=500000.0, vocab=512, ffn=512, places=64), "bfp8", 4),
+    "moe_top2": (dict(dim=256, heads=4, kv=2, layers=2, eps=1e-5, theta=10000.0, vocab=512, experts=8, k=2, moe=128, places=64), "experts", None),
+    "qwen_moe": (dict(dim=256, heads=4, kv=2, head_dim=128, layers=2, eps=1e-6, theta=1000000.0, vocab=512, experts=16, k=4, moe=64,
+                      places=64, qk_norm=True), "bfp8", 4),
+}
+
+
+def golden_model(name):
+    """(config, raw bf16 weights, quantised float32 weights) of a golden model case, regenerated from its seed."""
+    fields, mode, slots = MODELS[name]
+    c = llama.model(**fields)
+    raw = llama.synthetic(c, seed=11, norm_sigma=0.1, embed_sigma=1.0)
+    assert _checksum(raw) == str(golden("models.npz")[f"{name}.checksum"]), "seeded weights differ from the ones the fixture was made with"
+    return c, raw, llama.arrays(raw, llama.precision(c, mode)), slots
+
+
+@pytest.mark.parametrize("name", [n for n, v in MODELS.items() if v[2] is None])
+def test_forward_matches_reference_vectors(name):
+    g = golden("models.npz")
+    c, _, w, _ = golden_model(name)
+    ids, want, kv = g[f"{name}.ids"].tolist(), g[f"{name}.logits"], llama.kv_cache(c, 32)
+    for i in range(5):
+        new = ids[:5] if i == 0 else ids[4 + i:5 + i]
+        places = list(range(5)) if i == 0 else [4 + i]
+        got = llama.forward(new, places, w, c, kv)
+        assert np.allclose(got[0], want[i], rtol=1e-9, atol=1e-9), (name, i)
+
+
+@pytest.mark.parametrize("name", [n for n, v in MODELS.items() if v[2]])
+def test_batched_decode_matches_reference_vectors(name):
+    g = golden("models.npz")
+    c, _, w, slots = golden_model(name)
+    size, kv = 32, llama.kv_cache(c, 32 * slots)
+    for u, p in enumerate(g[f"{name}.prompts"]):
+        p = [int(t) for t in p if t >= 0]
+        part = [layer[:, u * size:(u + 1) * size] for layer in kv]
+        assert np.allclose(llama.forward(p, range(len(p)), w, c, part)[0], g[f"{name}.prefill"][u], rtol=1e-9, atol=1e-9)
+    for i in range(4):
+        got = llama.forward(g[f"{name}.step{i}.ids"].tolist(), g[f"{name}.step{i}.places"].tolist(), w, c, kv, slots)
+        assert np.allclose(got, g[f"{name}.steps"][i], rtol=1e-9, atol=1e-9), (name, i)

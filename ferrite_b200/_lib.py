@@ -19,6 +19,7 @@ _p, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_
 SIGNATURES = {
     "fb_version": (_i, []),
     "fb_last_error": (ctypes.c_char_p, []),
+    "fb_status_word": (_i, []),
     "fb_packed_bytes": (_sz, [_i, _i64, _i64]),
     "fb_quantize": (_i, [_i, _p, _i64, _i64, _i64, _p, _p]),
     "fb_dequantize": (_i, [_i, _p, _i64, _i64, _i64, _p, _p]),

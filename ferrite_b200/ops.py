@@ -64,6 +64,21 @@ def unpack_fields(p):
     return top, sign, mag
 
 
+_WORKSPACES = {}
+
+
+def linear_workspace(device, nbytes):
+    """The device's scratch buffer for fb_linear (split-K partial tiles, tile counters, the normalised
+    activations): one per device, zeroed when made (the counters start at 0 and every call leaves them 0),
+    grown when a call needs more.  Calls on one stream run in order, so they can share it."""
+    if not nbytes:
+        return None
+    have = _WORKSPACES.get(device)
+    if have is None or have.numel() < nbytes:
+        have = _WORKSPACES[device] = torch.zeros(max(nbytes, 64 << 20), dtype=torch.uint8, device=device)
+    return have
+
+
 def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="none", residual=None, workspace=None):
     """x [M, K] bf16 @ w (Packed, one matrix) with the fused RMSNorm prologue / SwiGLU or residual epilogue."""
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and w.batch == 1 and x.shape[1] == w.K, \
@@ -75,8 +90,7 @@ def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="no
         out = torch.empty(M, cols, dtype=_TORCH[out_dtype], device=x.device)
     assert out.shape == (M, cols) and out.stride(1) == 1 and out.dtype == _TORCH[out_dtype]
     if workspace is None:
-        need = lib().fb_linear_workspace_bytes(M, K, w.N)
-        workspace = torch.empty(need, dtype=torch.uint8, device=x.device) if need else None
+        workspace = linear_workspace(x.device, lib().fb_linear_workspace_bytes(M, K, w.N))
     check(lib().fb_linear(w.code, x.data_ptr(), M, K, x.stride(0), w.data.data_ptr(), w.N, out.data_ptr(), _lib.DTYPES[out_dtype],
                           out.stride(0), _ptr(norm_w), eps, epi, _ptr(residual), residual.stride(0) if residual is not None else 0,
                           _ptr(workspace), workspace.numel() if workspace is not None else 0, _stream()))

@@ -66,6 +66,9 @@ typedef enum {
 
 int fb_version(void);
 const char* fb_last_error(void);
+/* Device-side waits are bounded (ferrite gives every wait a timeout, ferrite/chip.py:78-82): a wait that gives up
+ * records a non-zero code here and the kernel returns.  Reads and clears it; synchronises with the device. */
+int fb_status_word(void);
 
 /* ---- block-float pack / unpack: Tensor.cast("bfp8"|"bfp4") (ferrite/tensor.py:315-320), the packer's
  * bfp8 cast (ferrite/compiler.py:52-70) and bfp4_kernel (ferrite/compiler.py:2038-2072); bit-exact with

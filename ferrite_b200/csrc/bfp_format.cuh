@@ -10,8 +10,27 @@
 
 namespace fb {
 
-__host__ __device__ inline int64_t mant_bytes(int fmt, int64_t K, int64_t N) { return fmt == FB_BFP8 ? K * N : K * N / 2; }
-__host__ __device__ inline int64_t packed_bytes(int fmt, int64_t K, int64_t N) { return mant_bytes(fmt, K, N) + K * (N / 16); }
+// A packed matrix is a grid of units: 64 rows of K (KSTEP) x 64 columns (a group of 4 runs).  A unit holds its
+// 4 x 64 runs' mantissas, run-major ([run][row][16 or 8 bytes]), then their 4 x 64 shared exponents ([run][row]);
+// the units of one column group follow each other along K, so any stretch of K of a 64-column group is one
+// contiguous piece of memory: one bulk copy per pipeline stage, and 128-bit loads for a lane walking down K.
+constexpr int KSTEP = 64, GROUP_RUNS = 4;
+__host__ __device__ constexpr int run_bytes(int fmt) { return fmt == FB_BFP8 ? 16 : 8; }
+__host__ __device__ constexpr int unit_mant_bytes(int fmt) { return GROUP_RUNS * KSTEP * run_bytes(fmt); }
+__host__ __device__ constexpr int unit_bytes(int fmt) { return unit_mant_bytes(fmt) + GROUP_RUNS * KSTEP; }
+__host__ __device__ inline int64_t ksteps_of(int64_t K) { return (K + KSTEP - 1) / KSTEP; }
+__host__ __device__ inline int64_t groups_of(int64_t N) { return (N + 16 * GROUP_RUNS - 1) / (16 * GROUP_RUNS); }
+__host__ __device__ inline int64_t packed_bytes(int fmt, int64_t K, int64_t N) { return groups_of(N) * ksteps_of(K) * unit_bytes(fmt); }
+// byte offsets of run b (= column / 16), row k inside a packed matrix
+__host__ __device__ inline int64_t unit_offset(int fmt, int64_t K, int64_t b, int64_t k) {
+  return ((b / GROUP_RUNS) * ksteps_of(K) + k / KSTEP) * unit_bytes(fmt);
+}
+__host__ __device__ inline int64_t mant_offset(int fmt, int64_t K, int64_t b, int64_t k) {
+  return unit_offset(fmt, K, b, k) + ((b % GROUP_RUNS) * KSTEP + k % KSTEP) * run_bytes(fmt);
+}
+__host__ __device__ inline int64_t exp_offset(int fmt, int64_t K, int64_t b, int64_t k) {
+  return unit_offset(fmt, K, b, k) + unit_mant_bytes(fmt) + (b % GROUP_RUNS) * KSTEP + k % KSTEP;
+}
 
 // Where a bfp4 value sits inside the 8 bytes of its (row, column block): column j of 16 is nibble
 // p of word h with j = 8h + 2*(p%4) + p/4, so that masking a word with 0x000F000F yields two neighbouring

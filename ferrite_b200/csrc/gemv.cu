@@ -14,9 +14,7 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
   const int grp = swiglu ? warp >> 2 : 0, wg = swiglu ? warp & 3 : warp;
   const int64_t NB = a.N / 16, K = a.K;
   const int64_t b = blockIdx.x + (grp ? NB / 2 : 0);
-  const uint8_t* W = static_cast<const uint8_t*>(a.W);
-  const uint8_t* mant = W + b * K * RunBytes<FMT>::value;
-  const uint8_t* exps = W + mant_bytes(FMT, K, a.N) + b * K;
+  const uint8_t* col = static_cast<const uint8_t*>(a.W) + (b / GROUP_RUNS) * ksteps_of(K) * unit_bytes(FMT);
 
   float acc[M][16], ss[M];
 #pragma unroll
@@ -25,7 +23,7 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) acc[t][j] = 0.f;
   }
-  gemv_accumulate<FMT, M, NORM>(mant, exps, static_cast<const uint16_t*>(a.x), a.ldx, static_cast<const uint16_t*>(a.norm_w), K,
+  gemv_accumulate<FMT, M, NORM>(col, (int)(b % GROUP_RUNS), static_cast<const uint16_t*>(a.x), a.ldx, static_cast<const uint16_t*>(a.norm_w), K,
                                 wg * 128, G * 128, acc, ss);
 
   __shared__ float red[8][M][16];

@@ -20,12 +20,15 @@ struct Raw4 {
   uint32_t tops;
 };
 
+// `col` points at the first unit of the run's column group, `run` is the run's place in the group (0..3)
 template <int FMT>
-__device__ __forceinline__ void load_raw4(Raw4<FMT>& r, const uint8_t* mant, const uint8_t* exps, int64_t k0) {
-  const uint4* p = reinterpret_cast<const uint4*>(mant + k0 * RunBytes<FMT>::value);
+__device__ __forceinline__ void load_raw4(Raw4<FMT>& r, const uint8_t* col, int run, int64_t k0) {
+  const uint8_t* unit = col + (k0 / KSTEP) * unit_bytes(FMT);
+  const int at = run * KSTEP + (int)(k0 % KSTEP);
+  const uint4* p = reinterpret_cast<const uint4*>(unit + at * RunBytes<FMT>::value);
 #pragma unroll
   for (int i = 0; i < (FMT == FB_BFP8 ? 4 : 2); ++i) r.q[i] = __ldg(p + i);
-  r.tops = __ldg(reinterpret_cast<const uint32_t*>(exps + k0));
+  r.tops = __ldg(reinterpret_cast<const uint32_t*>(unit + unit_mant_bytes(FMT) + at));
 }
 
 template <int FMT>
@@ -43,16 +46,16 @@ __device__ __forceinline__ void unpack_row(const Raw4<FMT>& r, int kk, uint32_t 
 // x rows are bf16 with M rows `ldx` apart; `g` (may be null) multiplies x along K (an RMSNorm's weight).
 // acc[t][j] += sum_k x[t][k] * g[k] * W[k][16b + j];  ss[t] += sum_k x[t][k]^2 over the rows this lane reads.
 template <int FMT, int M, bool NORM>
-__device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ mant, const uint8_t* __restrict__ exps,
+__device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ col, int run,
                                                 const uint16_t* __restrict__ x, int64_t ldx, const uint16_t* __restrict__ g,
                                                 int64_t K, int64_t k_first, int64_t k_step, float acc[M][16], float ss[M]) {
   const int lane = threadIdx.x & 31;
   int64_t k0 = k_first + 4 * lane;
   Raw4<FMT> cur, nxt;
-  if (k0 < K) load_raw4<FMT>(cur, mant, exps, k0);
+  if (k0 < K) load_raw4<FMT>(cur, col, run, k0);
   for (; k0 < K; k0 += k_step) {
     int64_t kn = k0 + k_step;
-    if (kn < K) load_raw4<FMT>(nxt, mant, exps, kn);
+    if (kn < K) load_raw4<FMT>(nxt, col, run, kn);
     float xv[M][4];
     float gv[4] = {1.f, 1.f, 1.f, 1.f};
     if (NORM) {

@@ -19,7 +19,6 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
   FB_REQUIRE(ldx >= K && ldx % 4 == 0 && ldo >= out_cols && (epilogue != FB_EPI_RESIDUAL || ldr >= N), "fb_linear: row strides too small or unaligned");
   FB_REQUIRE((uintptr_t)x % 8 == 0 && (uintptr_t)W % 16 == 0 && (uintptr_t)out % 4 == 0 && (!norm_w || (uintptr_t)norm_w % 8 == 0),
              "fb_linear: misaligned pointer");
-  FB_REQUIRE(fmt == FB_BFP8 || (K * N) % 32 == 0, "fb_linear: a bfp4 W has rows x cols a multiple of 32");
   fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, norm_w, eps, epilogue, residual, ldr, workspace, workspace_bytes};
   auto s = (cudaStream_t)stream;
   if (M > 4 && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);

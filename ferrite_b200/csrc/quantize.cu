@@ -31,8 +31,7 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
 #pragma unroll
   for (int j = 0; j < 16; ++j) top = max(top, (bits[j] >> 7) & 255u);
   uint8_t* base = dst + mat * packed_bytes(FMT, K, N);
-  uint8_t* exps = base + mant_bytes(FMT, K, N);
-  exps[b * K + k] = (uint8_t)top;
+  base[exp_offset(FMT, K, b, k)] = (uint8_t)top;
   if (FMT == FB_BFP8) {
     uint32_t out[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -43,7 +42,7 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
       uint32_t byte = q ? (((bits[j] >> 15) << 7) | q) : 0u;  // a zero carries no sign
       out[j >> 2] |= byte << (8 * (j & 3));
     }
-    *reinterpret_cast<uint4*>(base + (b * K + k) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+    *reinterpret_cast<uint4*>(base + mant_offset(FMT, K, b, k)) = make_uint4(out[0], out[1], out[2], out[3]);
   } else {
     uint32_t out[2] = {0, 0};
 #pragma unroll
@@ -54,7 +53,7 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
       uint32_t code = (bits[j] >> 15) ? 8u - q : 8u + q;
       out[j >> 3] |= code << (4 * bfp4_nibble_of_column(j & 7));
     }
-    *reinterpret_cast<uint2*>(base + (b * K + k) * 8) = make_uint2(out[0], out[1]);
+    *reinterpret_cast<uint2*>(base + mant_offset(FMT, K, b, k)) = make_uint2(out[0], out[1]);
   }
 }
 
@@ -62,10 +61,10 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
 template <int FMT>
 __device__ __forceinline__ void read_field(const uint8_t* base, int64_t K, int64_t b, int64_t k, int j, uint32_t& sign, uint32_t& mag) {
   if (FMT == FB_BFP8) {
-    uint32_t byte = base[(b * K + k) * 16 + j];
+    uint32_t byte = base[mant_offset(FMT, K, b, k) + j];
     sign = byte >> 7, mag = byte & 127u;
   } else {
-    uint32_t w = reinterpret_cast<const uint32_t*>(base + (b * K + k) * 8)[j >> 3];
+    uint32_t w = reinterpret_cast<const uint32_t*>(base + mant_offset(FMT, K, b, k))[j >> 3];
     int code = (int)((w >> (4 * bfp4_nibble_of_column(j & 7))) & 15u) - 8;
     sign = code < 0, mag = (uint32_t)(code < 0 ? -code : code);
   }
@@ -87,7 +86,7 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ src, uint16_t* __r
   if (idx >= batch * K * NB) return;
   int64_t b = idx % NB, k = (idx / NB) % K, mat = idx / (NB * K);
   const uint8_t* base = src + mat * packed_bytes(FMT, K, N);
-  uint32_t top = base[mant_bytes(FMT, K, N) + b * K + k];
+  uint32_t top = base[exp_offset(FMT, K, b, k)];
   uint32_t w[8];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
@@ -109,7 +108,7 @@ __global__ void fields_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
   if (idx >= batch * K * NB) return;
   int64_t b = idx % NB, k = (idx / NB) % K, mat = idx / (NB * K);
   const uint8_t* base = src + mat * packed_bytes(FMT, K, N);
-  top_out[(mat * K + k) * NB + b] = base[mant_bytes(FMT, K, N) + b * K + k];
+  top_out[(mat * K + k) * NB + b] = base[exp_offset(FMT, K, b, k)];
   for (int j = 0; j < 16; ++j) {
     uint32_t sign, mag;
     read_field<FMT>(base, K, b, k, j, sign, mag);
@@ -122,8 +121,6 @@ static int check_shape(int fmt, int64_t batch, int64_t K, int64_t N) {
   FB_REQUIRE(fmt == FB_BFP8 || fmt == FB_BFP4, "a block float is bfp8 or bfp4, not dtype %d", fmt);
   FB_REQUIRE(batch >= 1 && K >= 1 && N >= 16 && N % 16 == 0, "a block float's rows are runs of 16: got %lld x %lld x %lld",
              (long long)batch, (long long)K, (long long)N);
-  FB_REQUIRE(fmt == FB_BFP8 || (K * N) % 32 == 0, "bfp4 planes are 16-byte aligned: rows x cols must be a multiple of 32");
-  FB_REQUIRE(batch == 1 || (K * N) % 256 == 0, "a batch of block floats keeps each matrix 16-byte aligned: rows x cols must be a multiple of 256");
   return FB_OK;
 }
 
@@ -140,6 +137,10 @@ extern "C" int fb_quantize(int fmt, const void* src, int64_t batch, int64_t K, i
   int64_t total = batch * K * (N / 16);
   dim3 grid((unsigned)fb::ceil_div(total, 256)), block(256);
   auto s = (cudaStream_t)stream;
+  if (K % fb::KSTEP || N % (16 * fb::GROUP_RUNS)) {  // the padding of the last units holds zeros (bfp4's zero is the code 8)
+    if (cudaMemsetAsync(dst, fmt == FB_BFP8 ? 0 : 0x88, (size_t)batch * fb::packed_bytes(fmt, K, N), s) != cudaSuccess)
+      return fb::launch_status("fb_quantize (padding)");
+  }
   if (fmt == FB_BFP8) fb::quantize_kernel<FB_BFP8><<<grid, block, 0, s>>>((const uint16_t*)src, (uint8_t*)dst, batch, K, N);
   else fb::quantize_kernel<FB_BFP4><<<grid, block, 0, s>>>((const uint16_t*)src, (uint8_t*)dst, batch, K, N);
   return fb::launch_status("fb_quantize");

@@ -30,15 +30,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Wait for the phase with `parity` to complete.  Bounded: after WAIT_CLOCKS it records `code` in the status
-// word, raises the CTA's abort flag (every later wait then returns at once) and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (*abort_flag) return false;
+// word, raises the CTA's abort flag (a word of shared memory; every later wait then returns at once) and
+// returns false.
+__device__ __forceinline__ uint32_t ld_shared_volatile(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_flag, int code) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (ld_shared_volatile(abort_flag)) return false;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
+    if (ld_shared_volatile(abort_flag)) return false;
     if (clock64() - start > WAIT_CLOCKS) {
-      *abort_flag = 1;
+      asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
       atomicCAS(&g_status_word, 0, code);
       return false;
     }

@@ -22,15 +22,19 @@
  * shares the largest biased bf16 exponent of the run (`top`), every value keeps a sign and
  * a 7-bit (bfp8) or 3-bit (bfp4) magnitude, value = +-mag * 2^(top-133) (bfp4: mag*16).
  * The footprint is ferrite's too: 1088 / 576 bytes per 1024 values.  The byte ORDER is
- * this library's own (ferrite's is its 32x32 Tensix tile with 16x16 faces):
- *     plane 0, offset 0:            mantissas, for column block b = n/16 and row k:
- *                                     bfp8: 16 bytes at (b*K + k)*16, byte j = sign<<7 | mag
- *                                           for column 16b + j;
- *                                     bfp4:  8 bytes at (b*K + k)*8 read as two little-endian
- *                                           32-bit words; nibble p (bits 4p..4p+3) of word h
- *                                           holds column 16b + 8h + 2*(p%4) + p/4 as the
- *                                           excess-8 code 8 + (sign ? -mag : mag);
- *     plane 1, offset K*N*(1 | 1/2): shared exponents, one byte at b*K + k.
+ * this library's own (ferrite's is its 32x32 Tensix tile with 16x16 faces): a matrix is a
+ * grid of UNITS of 64 rows of K x 64 columns (4 runs); rows and columns are padded with
+ * zeros up to whole units (ferrite pads its tiles the same way, ferrite/tensor.py:22-24).
+ *     unit (g, s) for column group g = n/64 and row step s = k/64 lies at byte
+ *       (g * ceil(K/64) + s) * U,   U = 4352 (bfp8) or 2304 (bfp4);
+ *     the units of one column group follow each other along K, so a stretch of K of one
+ *     group is one contiguous piece of memory;
+ *     inside a unit, for run r = (n/16)%4 and row i = k%64:
+ *       mantissas  bfp8: 16 bytes at (r*64 + i)*16, byte j = sign<<7 | mag for column 16*(n/16) + j;
+ *                  bfp4:  8 bytes at (r*64 + i)*8 read as two little-endian 32-bit words;
+ *                         nibble p (bits 4p..4p+3) of word h holds column 8h + 2*(p%4) + p/4
+ *                         of the run as the excess-8 code 8 + (sign ? -mag : mag);
+ *       exponents  one byte at 4*64*(16|8) + r*64 + i.
  *   A zero magnitude is stored without a sign (as ferrite stores it).  fb_unpack_fields
  *   returns (top, sign, mag) per value for checking against the reference model.
  *   A batch of matrices (a mixture's experts) is that many packed matrices back to back,
@@ -88,8 +92,9 @@ int fb_unpack_fields(int fmt, const void* packed, int64_t batch, int64_t K, int6
  *   acc = h @ W, fp32 accumulation, W packed [K, N] in `fmt` (FB_BFP8, FB_BFP4 or FB_BF16 row-major)
  *   epilogue (fb_epilogue), out dtype FB_BF16 or FB_FP32 (fp32: the output layer, models/llama.py:479)
  * out is [M, N] (or [M, N/2] after FB_EPI_SWIGLU), row stride ldo elements.
- * M <= 8 runs as a bandwidth-bound GEMV on CUDA cores; larger M on tcgen05 tensor cores.
- * workspace: fb_linear_workspace_bytes(M, K, N) bytes of device scratch (may be 0 / NULL). */
+ * M <= 4 runs as a bandwidth-bound GEMV on CUDA cores; larger M on tcgen05 tensor cores.
+ * workspace: fb_linear_workspace_bytes(M, K, N) bytes of device scratch (0 / NULL when that is 0):
+ * it holds the normalised activations of the RMSNorm prologue between the two kernels of a call. */
 size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out,
               int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,

@@ -25,7 +25,9 @@ def test_every_declared_symbol_is_exported_and_bound():
 def test_host_side_calls():
     lib = _lib.lib()
     assert lib.fb_version() >= 1
-    assert lib.fb_packed_bytes(_lib.BFP8, 32, 32) == 1088 and lib.fb_packed_bytes(_lib.BFP4, 32, 32) == 576  # ferrite/compiler.py:19-20
+    # ferrite's footprint, 1088 / 576 bytes per 1024 values (ferrite/compiler.py:19-20), in units of 64 x 64
+    assert lib.fb_packed_bytes(_lib.BFP8, 64, 64) == 4 * 1088 and lib.fb_packed_bytes(_lib.BFP4, 128, 64) == 8 * 576
+    assert lib.fb_packed_bytes(_lib.BFP8, 32, 48) == 4 * 1088, "rows and columns pad to whole units"
     assert lib.fb_packed_bytes(_lib.BFP8, 32, 40) == 0, "columns come in runs of 16"
 
 

@@ -17,7 +17,8 @@ def test_cast_is_bit_exact_against_reference_vectors(cuda, fmt, name):
     g = golden("bfp.npz")
     bits = g[f"{name}.bits"]
     packed = ops.quantize(bits_to_tensor(bits, cuda), fmt)
-    assert packed.data.numel() == bits.size * (17 if fmt == "bfp8" else 9) // 16  # 1088 / 576 bytes per 1024 values
+    units = -(-bits.shape[0] // 64) * -(-bits.shape[1] // 64)
+    assert packed.data.numel() == units * 4 * (1088 if fmt == "bfp8" else 576)  # ferrite's bytes per 1024 values, whole 64 x 64 units
     got = to_numpy(ops.dequantize(packed))[0]
     want = g[f"{name}.{fmt}"]
     assert np.array_equal(got, want), f"{name}: {np.count_nonzero(got != want)} of {want.size} values differ"

@@ -1,0 +1,284 @@
+// Decode attention over a bf16 KV cache: softmax(q k^T / sqrt(hd) + mask) v for one new token per sequence
+// (models/llama.py:111-146; ferrite's one-kernel attention Tensor.attend, ferrite/tensor.py:487-516,
+// ferrite/compiler.py:1147-1170).  The mask is never materialised: each token carries the first cache row of its
+// sequence (`base`) and its place; it sees keys base .. base + place (and, with a sliding window, only the last
+// `window` of them), which is what ferrite's places-based mask means.
+//
+// Bandwidth-bound on the KV read, so the work is laid out to read every key and value row exactly once:
+//   CTA = (token, kv head, split of the keys); the kv head's `rep` query heads are the rows of one 16-row MMA tile
+//   (grouped-query attention shares each key row among them, as ferrite's batch entry per (kv head, sequence) does);
+//   4 warps take 16 keys each of a 64-key tile staged by cp.async (double-buffered, XOR-swizzled rows);
+//   q k^T and p v run on mma.sync m16n8k16 (bf16 in, fp32 accumulate) with an online softmax in registers.
+// Keys are split across CTAs (flash-decoding) so that few sequences still fill the GPU; a second small kernel
+// merges the splits by their running maxima, as ferrite merges its `parts` (ferrite/tensor.py:511-516).
+#include "common.cuh"
+
+namespace fb {
+
+struct AttnArgs {
+  const uint16_t* q;  // [T, H * hd]
+  int64_t ld_q;
+  const uint16_t* cache;  // [2 KV, cache_rows, hd]: keys' heads then values'
+  int64_t cache_rows;
+  const int32_t *base, *place;  // [T]
+  int window;
+  int H, KV;
+  float scale_log2;  // log2(e) / sqrt(hd)
+  uint16_t* out;     // [T, H * hd]
+  int64_t ld_o;
+  float* part_o;   // [T * KV, splits, 16, hd]
+  float* part_ml;  // [T * KV, splits, 16, 2]
+  int splits;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t r[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t r[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int ATT_THREADS = 128, KEY_TILE = 64;
+
+// byte offset of 16-byte chunk `ch` of row `r` in a tile whose rows are HD bf16 wide (chunks XOR-swizzled by row)
+template <int HD>
+__device__ __forceinline__ uint32_t tile_off(int r, int ch) { return (uint32_t)(r * HD * 2 + ((ch ^ (r & 7)) << 4)); }
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs a) {
+  constexpr int CH = HD / 8;               // 16-byte chunks per row
+  constexpr int TILE_BYTES = KEY_TILE * HD * 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;                      // [16][HD] bf16
+  uint8_t* sK = sQ + 16 * HD * 2;          // 2 x [64][HD]
+  uint8_t* sV = sK + 2 * TILE_BYTES;       // 2 x [64][HD]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = blockIdx.x / a.KV, g = blockIdx.x % a.KV, split = blockIdx.y;
+  const int rep = a.H / a.KV;
+
+  // the keys this CTA reads: the token's visible range, cut into `splits` runs of whole tiles
+  const int len = a.place[t] + 1;
+  const int first = a.window > 0 ? max(0, len - a.window) : 0;
+  const int per = ((len - first + a.splits - 1) / a.splits + KEY_TILE - 1) / KEY_TILE * KEY_TILE;
+  const int k0 = first + split * per, k1 = min(len, k0 + per);
+  const int n_tiles = k1 > k0 ? (k1 - k0 + KEY_TILE - 1) / KEY_TILE : 0;
+  const uint16_t* Kg = a.cache + ((int64_t)g * a.cache_rows + a.base[t]) * HD;
+  const uint16_t* Vg = a.cache + ((int64_t)(a.KV + g) * a.cache_rows + a.base[t]) * HD;
+
+  auto load_tile = [&](int i, int buf) {
+    const int key0 = k0 + i * KEY_TILE;
+    for (int c = tid; c < KEY_TILE * CH; c += ATT_THREADS) {
+      const int r = c / CH, ch = c % CH;
+      const int key = min(key0 + r, k1 - 1);  // rows past the end repeat the last key; their scores are masked
+      cp_async16(smem_addr(sK + buf * TILE_BYTES) + tile_off<HD>(r, ch), Kg + (int64_t)key * HD + ch * 8);
+      cp_async16(smem_addr(sV + buf * TILE_BYTES) + tile_off<HD>(r, ch), Vg + (int64_t)key * HD + ch * 8);
+    }
+    cp_async_commit();
+  };
+  if (n_tiles) load_tile(0, 0);
+
+  // the kv head's query heads as rows 0..rep-1 of a 16-row tile, the rest zeros
+  for (int c = tid; c < 16 * CH; c += ATT_THREADS) {
+    const int r = c / CH, ch = c % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rep) v = *reinterpret_cast<const uint4*>(a.q + t * a.ld_q + (int64_t)(g * rep + r) * HD + ch * 8);
+    *reinterpret_cast<uint4*>(sQ + tile_off<HD>(r, ch)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kt = 0; kt < HD / 16; ++kt) {
+    const int m = lane >> 3, r = (m & 1) * 8 + (lane & 7), ch = 2 * kt + (m >> 1);
+    ldmatrix_x4(smem_addr(sQ) + tile_off<HD>(r, ch), qf[kt]);
+  }
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows lane/4 and lane/4 + 8
+
+  for (int i = 0; i < n_tiles; ++i) {
+    const int buf = i & 1;
+    if (i + 1 < n_tiles) load_tile(i + 1, buf ^ 1);
+    if (i + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    const uint32_t kt_base = smem_addr(sK + buf * TILE_BYTES), vt_base = smem_addr(sV + buf * TILE_BYTES);
+    const int krow = 16 * warp;  // this warp's 16 keys of the tile
+
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kt = 0; kt < HD / 16; ++kt) {
+      uint32_t b[4];
+      const int m = lane >> 3, r = krow + (m >> 1) * 8 + (lane & 7), ch = 2 * kt + (m & 1);
+      ldmatrix_x4(kt_base + tile_off<HD>(r, ch), b);
+      mma_bf16(s[0], qf[kt], b[0], b[1]);
+      mma_bf16(s[1], qf[kt], b[2], b[3]);
+    }
+    // scores -> probabilities under the running maximum of each row
+    const int key_first = k0 + i * KEY_TILE + krow + (lane & 3) * 2;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key_first + nt * 8 + (e & 1);
+        s[nt][e] = key < k1 ? s[nt][e] * a.scale_log2 : -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = exp2f(m_run[h] - m_safe);  // (-inf - finite = -inf: 0)
+      m_run[h] = m_new;
+      l_run[h] *= corr[h];
+      mx[h] = m_safe;
+    }
+    uint32_t pf[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float p0 = exp2f(s[nt][0] - mx[0]), p1 = exp2f(s[nt][1] - mx[0]);
+      const float p2 = exp2f(s[nt][2] - mx[1]), p3 = exp2f(s[nt][3] - mx[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      pf[2 * nt] = pack_bf16x2(p0, p1);
+      pf[2 * nt + 1] = pack_bf16x2(p2, p3);
+    }
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; dt += 2) {
+      o[dt][0] *= corr[0], o[dt][1] *= corr[0], o[dt][2] *= corr[1], o[dt][3] *= corr[1];
+      o[dt + 1][0] *= corr[0], o[dt + 1][1] *= corr[0], o[dt + 1][2] *= corr[1], o[dt + 1][3] *= corr[1];
+      uint32_t b[4];
+      const int m = lane >> 3, r = krow + (m & 1) * 8 + (lane & 7), ch = dt + (m >> 1);
+      ldmatrix_x4_trans(vt_base + tile_off<HD>(r, ch), b);
+      mma_bf16(o[dt], pf, b[0], b[1]);
+      mma_bf16(o[dt + 1], pf, b[2], b[3]);
+    }
+    __syncthreads();  // the buffer is free for the load after next
+  }
+
+  // ---- merge the four warps' partial softmaxes (each saw different keys) through shared memory
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  float* so = reinterpret_cast<float*>(sK);           // [4][16][HD]
+  float* sml = reinterpret_cast<float*>(sV);          // [4][16][2]
+#pragma unroll
+  for (int dt = 0; dt < HD / 8; ++dt) {
+    const int col = dt * 8 + (lane & 3) * 2, r = lane >> 2;
+    *reinterpret_cast<float2*>(so + (warp * 16 + r) * HD + col) = make_float2(o[dt][0], o[dt][1]);
+    *reinterpret_cast<float2*>(so + (warp * 16 + r + 8) * HD + col) = make_float2(o[dt][2], o[dt][3]);
+  }
+  if ((lane & 3) == 0) {
+    sml[(warp * 16 + (lane >> 2)) * 2] = m_run[0], sml[(warp * 16 + (lane >> 2)) * 2 + 1] = l_run[0];
+    sml[(warp * 16 + (lane >> 2) + 8) * 2] = m_run[1], sml[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rep * HD; idx += ATT_THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sml[(w * 16 + r) * 2]);
+    const float m_safe = m == -INFINITY ? 0.f : m;
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(sml[(w * 16 + r) * 2] - m_safe);
+      l += sml[(w * 16 + r) * 2 + 1] * f;
+      acc += so[(w * 16 + r) * HD + d] * f;
+    }
+    if (a.splits == 1) {
+      a.out[t * a.ld_o + (int64_t)(g * rep + r) * HD + d] = (uint16_t)float_to_bf16_bits(l > 0.f ? acc / l : 0.f);
+    } else {
+      const int64_t at = ((int64_t)blockIdx.x * a.splits + split) * 16 + r;
+      a.part_o[at * HD + d] = acc;
+      if (d == 0) a.part_ml[at * 2] = m, a.part_ml[at * 2 + 1] = l;
+    }
+  }
+}
+
+// one block per (token, query head): weight each split by exp2(its max - the overall max), sum, divide
+template <int HD>
+__global__ void __launch_bounds__(HD) attention_combine_kernel(AttnArgs a) {
+  const int t = blockIdx.x / a.H, h = blockIdx.x % a.H, d = threadIdx.x;
+  const int rep = a.H / a.KV, g = h / rep, r = h % rep;
+  const int64_t first = ((int64_t)(t * a.KV + g) * a.splits) * 16 + r;
+  float m = -INFINITY;
+  for (int s = 0; s < a.splits; ++s) m = fmaxf(m, a.part_ml[(first + s * 16) * 2]);
+  const float m_safe = m == -INFINITY ? 0.f : m;
+  float l = 0.f, acc = 0.f;
+  for (int s = 0; s < a.splits; ++s) {
+    const float f = exp2f(a.part_ml[(first + s * 16) * 2] - m_safe);
+    l += a.part_ml[(first + s * 16) * 2 + 1] * f;
+    acc += a.part_o[(first + s * 16) * HD + d] * f;
+  }
+  a.out[t * a.ld_o + (int64_t)h * HD + d] = (uint16_t)float_to_bf16_bits(l > 0.f ? acc / l : 0.f);
+}
+
+static int pick_splits(int64_t T, int KV, int64_t max_keys) {
+  const int64_t ctas = T * KV;
+  int64_t want = (4 * 148 + ctas - 1) / ctas;               // about four CTAs per SM in flight
+  const int64_t most = (max_keys + 2 * KEY_TILE - 1) / (2 * KEY_TILE);  // at least two tiles per split
+  want = want > most ? most : want;
+  return (int)(want < 1 ? 1 : want > 32 ? 32 : want);
+}
+
+}  // namespace fb
+
+extern "C" size_t fb_decode_attention_workspace_bytes(int64_t T, int H, int KV, int hd, int64_t max_keys) {
+  (void)H;
+  const int splits = fb::pick_splits(T, KV, max_keys);
+  return splits == 1 ? 0 : (size_t)T * KV * splits * 16 * (hd + 2) * sizeof(float);
+}
+
+extern "C" int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
+                                   const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+  FB_REQUIRE(q && cache && base && place && out && T >= 1, "fb_decode_attention: null pointer or no tokens");
+  FB_REQUIRE(hd == 64 || hd == 128, "fb_decode_attention: heads of 64 or 128 columns (got %d)", hd);
+  FB_REQUIRE(KV >= 1 && H % KV == 0 && H / KV <= 16, "fb_decode_attention: up to 16 query heads per key head (got %d / %d)", H, KV);
+  FB_REQUIRE(ld_q >= (int64_t)H * hd && ld_o >= (int64_t)H * hd && ld_q % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)cache % 16 == 0,
+             "fb_decode_attention: rows of q 16-byte aligned");
+  FB_REQUIRE(max_keys >= 1 && max_keys <= cache_rows && window >= 0, "fb_decode_attention: max_keys within the cache");
+  const int splits = fb::pick_splits(T, KV, max_keys);
+  const size_t need = splits == 1 ? 0 : (size_t)T * KV * splits * 16 * (hd + 2) * sizeof(float);
+  if (need && (!workspace || workspace_bytes < need)) {
+    fb::set_error("fb_decode_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return FB_ERR_MEMORY;
+  }
+  fb::AttnArgs a{(const uint16_t*)q, ld_q, (const uint16_t*)cache, cache_rows, base, place, window, H, KV,
+                 1.4426950408889634f / sqrtf((float)hd), (uint16_t*)out, ld_o, (float*)workspace,
+                 (float*)workspace + (size_t)T * KV * splits * 16 * hd, splits};
+  auto s = (cudaStream_t)stream;
+  dim3 grid((unsigned)(T * KV), (unsigned)splits);
+  const size_t smem = (size_t)(16 + 4 * fb::KEY_TILE) * hd * 2;
+  if (hd == 128) {
+    static bool once = false;
+    if (!once) cudaFuncSetAttribute(fb::decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
+    fb::decode_attention_kernel<128><<<grid, fb::ATT_THREADS, smem, s>>>(a);
+    if (splits > 1) fb::attention_combine_kernel<128><<<(unsigned)(T * H), 128, 0, s>>>(a);
+  } else {
+    static bool once = false;
+    if (!once) cudaFuncSetAttribute(fb::decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
+    fb::decode_attention_kernel<64><<<grid, fb::ATT_THREADS, smem, s>>>(a);
+    if (splits > 1) fb::attention_combine_kernel<64><<<(unsigned)(T * H), 64, 0, s>>>(a);
+  }
+  return fb::launch_status("fb_decode_attention");
+}

@@ -23,6 +23,8 @@ int launch_status(const char* what);  // cudaGetLastError() -> FB_OK / FB_ERR_LA
 
 __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 
 // float -> bf16 bits, round to nearest even (what an upload of Python floats does: ferrite/tensor.py:56)

@@ -4,10 +4,11 @@
 // tokens are its N dimension, so a decode batch of 32 tokens costs one 128x32x16 tcgen05.mma per 16 rows of K and
 // the kernel stays bound by the HBM stream of packed weights, which it reads exactly once:
 //
-//   raw producer (1 thread)  cp.async.bulk: 128 rows of K of two 64-column groups = two contiguous pieces -> smem ring
-//   x producer   (1 thread)  TMA tile [tokens x 64] of the (normalised) activations, 128B-swizzled      -> smem ring
-//   8 worker warps           raw bytes -> bf16 pairs in registers (bfp_format.cuh) -> MN-major 128B-swizzled A tiles
-//   MMA issuer   (1 thread)  4 x tcgen05.mma (K = 16 each) per 64 rows, accumulating in TMEM; tcgen05.commit frees slots
+//   x producer   (1 thread)  TMA tiles [tokens x 64] of the (normalised) activations, 128B-swizzled     -> smem ring
+//   16 worker warps          packed bytes: 128-bit global loads issued three steps ahead (registers, no staging in
+//                            shared memory: its bandwidth is what the bf16 operand tiles need) -> bf16 pairs
+//                            (bfp_format.cuh) -> MN-major 128B-swizzled A tiles
+//   MMA issuer   (1 thread)  8 x tcgen05.mma (K = 16 each) per 128 rows, accumulating in TMEM; tcgen05.commit frees slots
 //   epilogue (worker warps)  tcgen05.ld -> shared memory -> RMSNorm row scale, SwiGLU / residual, bf16 / fp32 store
 //
 // Few column tiles (N = 4096 gives 32) cannot fill 148 SMs, so K is split across the CTAs of a thread-block cluster
@@ -15,6 +16,8 @@
 // shared memory, and it adds them in rank order (deterministic) before the epilogue.  No global scratch is needed for
 // the reduction.  Every mbarrier wait is bounded (sm100.cuh).
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "bfp_format.cuh"
 #include "linear.cuh"
@@ -24,12 +27,14 @@ namespace fb {
 
 namespace {
 
-constexpr int TILE_N = 128;   // output columns per CTA (MMA M): two 64-column groups
-constexpr int STAGE_STEPS = 2;  // 64-row units of K per raw stage
-constexpr int WORKERS = 256;
-constexpr int WARP_RAW = 8, WARP_MMA = 9, WARP_X = 10;
-constexpr int THREADS = 11 * 32;
-constexpr int A_SLOT_BYTES = TILE_N * KSTEP * 2;
+constexpr int TILE_N = 128;     // output columns per CTA (MMA M): two 64-column groups
+constexpr int STEP_UNITS = 2;   // 64-row units of K per pipeline step: 128 rows
+constexpr int STEP_ROWS = STEP_UNITS * KSTEP;
+constexpr int WORKERS = 512;    // one CTA per SM (a kernel that allocates tensor memory gets the SM to itself)
+constexpr int WARP_MMA = 16, WARP_X = 17;
+constexpr int THREADS = 18 * 32;
+constexpr int AHEAD = 3;        // steps of K a worker's loads run ahead of its unpacking
+constexpr int A_SLOT_BYTES = TILE_N * STEP_ROWS * 2;
 constexpr int MAX_STAGES = 8;
 constexpr int WS_RSTD = 1024;  // workspace: row scales, then the normalised activations
 
@@ -37,12 +42,12 @@ struct GemmParams {
   LinearArgs a;
   int nt;  // MMA N: tokens rounded up to a multiple of 16
   int tmem_cols;
-  int splits, steps_per_split, steps_total;  // K in units of 64 rows
-  int raw_stages, x_slots, a_slots;
+  int splits, steps_per_split, steps_total;  // K in steps of 128 rows
+  int x_slots, a_slots;
   const float* rstd;  // [M] row scales of the RMSNorm prologue, or null
 };
 
-enum WaitCode { WAIT_RAW_EMPTY = 101, WAIT_RAW_FULL, WAIT_X_EMPTY, WAIT_X_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_ACC };
+enum WaitCode { WAIT_X_EMPTY = 103, WAIT_X_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_ACC };
 
 // a ring position: slot index and the parity of the phase its barriers are in (no division in the loops)
 struct Ring {
@@ -65,28 +70,26 @@ __device__ __forceinline__ void store_remote_f32(uint32_t local_addr, uint32_t r
 template <int FMT>
 __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   constexpr int UNIT = unit_bytes(FMT), UNIT_MANT = unit_mant_bytes(FMT), RUN = run_bytes(FMT);
-  constexpr int RAW_STAGE = 2 * STAGE_STEPS * UNIT;  // [group][step][unit]
   extern __shared__ uint8_t smem_unaligned[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int tile = blockIdx.x, split = blockIdx.y;
-  const int nt = p.nt, R = p.raw_stages, SX = p.x_slots, SA = p.a_slots;
+  const int nt = p.nt, SX = p.x_slots, SA = p.a_slots;
   const LinearArgs& a = p.a;
   const bool swiglu = a.epilogue == FB_EPI_SWIGLU;
   const int64_t K = a.K, KS = ksteps_of(K), G = groups_of(a.N);
 
   uint8_t* sA = smem;  // A slots; reused as the split-K exchange buffer once the MMAs are done
+  const int x_slot_bytes = STEP_UNITS * nt * 128;  // a [tokens x 64] tile per 64 rows of K
   uint8_t* sX = sA + SA * A_SLOT_BYTES;
-  uint8_t* sRaw = sX + SX * nt * 128;
-  uint2* lut = reinterpret_cast<uint2*>(sRaw + R * RAW_STAGE);  // exponent byte -> {scale, -offset * scale} bf16 pairs
+  uint2* lut = reinterpret_cast<uint2*>(sX + SX * x_slot_bytes);  // exponent byte -> {scale, -offset * scale} bf16 pairs
   uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 256);
-  uint64_t* raw_full = bars, *raw_empty = bars + MAX_STAGES, *x_full = bars + 2 * MAX_STAGES, *x_empty = bars + 3 * MAX_STAGES;
-  uint64_t* a_full = bars + 4 * MAX_STAGES, *a_empty = bars + 5 * MAX_STAGES, *acc_full = bars + 6 * MAX_STAGES;
+  uint64_t* x_full = bars, *x_empty = bars + MAX_STAGES, *a_full = bars + 2 * MAX_STAGES, *a_empty = bars + 3 * MAX_STAGES;
+  uint64_t* acc_full = bars + 4 * MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   const uint32_t abort_flag = smem_u32(tmem_slot + 1);
 
   if (tid == 0) {
-    for (int s = 0; s < R; ++s) mbar_init(smem_u32(raw_full + s), 1), mbar_init(smem_u32(raw_empty + s), WORKERS / 32);
     for (int s = 0; s < SX; ++s) mbar_init(smem_u32(x_full + s), 1), mbar_init(smem_u32(x_empty + s), 1);
     for (int s = 0; s < SA; ++s) mbar_init(smem_u32(a_full + s), WORKERS / 32), mbar_init(smem_u32(a_empty + s), 1);
     mbar_init(smem_u32(acc_full), 1);
@@ -105,31 +108,21 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
 
   const int s0 = split * p.steps_per_split;
   const int n_steps = min(p.steps_total - s0, p.steps_per_split);
-  const int n_stages = (n_steps + STAGE_STEPS - 1) / STAGE_STEPS;
+  const int units_total = (int)KS;  // the last step of K may hold one unit only
 
   // the tile's two 64-column groups: neighbours, or a group of gate columns and the group of their up columns
   const int64_t g0 = swiglu ? tile : 2 * (int64_t)tile, g1 = swiglu ? tile + G / 2 : 2 * (int64_t)tile + 1;
   const bool has_g1 = g1 < G;
 
-  if (warp == WARP_RAW && lane == 0) {
-    const uint8_t* W = static_cast<const uint8_t*>(a.W);
-    Ring rr;
-    for (int i = 0; i < n_stages; ++i, rr.next(R)) {
-      const int r = rr.slot, steps = min(STAGE_STEPS, n_steps - i * STAGE_STEPS);
-      mbar_wait(smem_u32(raw_empty + r), rr.phase ^ 1, abort_flag, WAIT_RAW_EMPTY);
-      const uint32_t bar = smem_u32(raw_full + r), dst = smem_u32(sRaw + r * RAW_STAGE);
-      const int64_t first = s0 + (int64_t)i * STAGE_STEPS;
-      mbar_expect_tx(bar, (has_g1 ? 2 : 1) * steps * UNIT);
-      bulk_copy_g2s(dst, W + (g0 * KS + first) * UNIT, steps * UNIT, bar);
-      if (has_g1) bulk_copy_g2s(dst + STAGE_STEPS * UNIT, W + (g1 * KS + first) * UNIT, steps * UNIT, bar);
-    }
-  } else if (warp == WARP_X && lane == 0) {
+  if (warp == WARP_X && lane == 0) {
     Ring rx;
     for (int i = 0; i < n_steps; ++i, rx.next(SX)) {
       const int s = rx.slot;
       mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
-      mbar_expect_tx(smem_u32(x_full + s), nt * 128);
-      tma_load_2d(smem_u32(sX + s * nt * 128), &tmap_x, (s0 + i) * KSTEP, 0, smem_u32(x_full + s));
+      mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
+#pragma unroll
+      for (int u = 0; u < STEP_UNITS; ++u)  // rows of K past the end read as zeros
+        tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, ((s0 + i) * STEP_UNITS + u) * KSTEP, 0, smem_u32(x_full + s));
     }
   } else if (warp == WARP_MMA && lane == 0) {
     const uint32_t idesc = umma_idesc_bf16(nt, true, false);
@@ -137,7 +130,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     // X: K-major, one 128-byte swizzled row per token, groups of 8 tokens 1024 B apart; 32 bytes of K per MMA
     // The address field is the low 14 bits (units of 16 B): slots and K offsets are added to it directly.
     const uint64_t da0 = umma_smem_desc(smem_u32(sA), 1024, 2048), dx0 = umma_smem_desc(smem_u32(sX), 16, 1024);
-    const uint32_t x_slot16 = (uint32_t)(nt * 128) >> 4;
+    const uint32_t x_slot16 = (uint32_t)x_slot_bytes >> 4, x_unit16 = (uint32_t)(nt * 128) >> 4;
     Ring ra, rx;
     for (int i = 0; i < n_steps; ++i, ra.next(SA), rx.next(SX)) {
       mbar_wait(smem_u32(a_full + ra.slot), ra.phase, abort_flag, WAIT_A_FULL);
@@ -145,66 +138,96 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       tc_fence_after();
       const uint64_t da = da0 + (uint32_t)ra.slot * (A_SLOT_BYTES >> 4), dx = dx0 + (uint32_t)rx.slot * x_slot16;
 #pragma unroll
-      for (int kk = 0; kk < KSTEP / 16; ++kk) umma_bf16(tmem, da + kk * (4096 >> 4), dx + kk * (32 >> 4), idesc, (i | kk) != 0);
+      for (int kk = 0; kk < STEP_ROWS / 16; ++kk)
+        umma_bf16(tmem, da + kk * (4096 >> 4), dx + (kk >> 2) * x_unit16 + (kk & 3) * (32 >> 4), idesc, (i | kk) != 0);
       umma_commit(smem_u32(a_empty + ra.slot));
       umma_commit(smem_u32(x_empty + rx.slot));
     }
     umma_commit(smem_u32(acc_full));
   } else if (warp < WORKERS / 32) {
-    // this thread's two (run, row) places in every 64-row step, and where their 16 columns go in the A slot
-    uint32_t raw_off[2], exp_off[2], a_off[2][2];
+    // this thread's two (run, row) places in every 128-row step: where their bytes lie in the step's units of the
+    // packed matrix, and where their 16 columns go in the A slot
+    const uint8_t* W = static_cast<const uint8_t*>(a.W);
+    const uint8_t* src[2];
+    uint32_t exp_rel[2], a_off[2][2];
+    bool col_ok[2];
+    int unit_of[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      const int u = tid + WORKERS * j, run8 = u >> 6, k = u & 63, grp = run8 >> 2, run = run8 & 3;
-      raw_off[j] = grp * (STAGE_STEPS * UNIT) + (run * KSTEP + k) * RUN;
-      exp_off[j] = grp * (STAGE_STEPS * UNIT) + UNIT_MANT + run * KSTEP + k;
+      const int u = tid + WORKERS * j, run8 = u >> 7, k = u & 127, grp = run8 >> 2, run = run8 & 3;
+      const int unit = k >> 6, ku = k & 63;
+      unit_of[j] = unit;
+      col_ok[j] = grp == 0 || has_g1;
+      src[j] = W + ((grp ? g1 : g0) * KS + (int64_t)s0 * STEP_UNITS + unit) * UNIT + (run * KSTEP + ku) * RUN;
+      exp_rel[j] = UNIT_MANT + run * KSTEP + ku - (run * KSTEP + ku) * RUN;
       const int slot = swiglu ? (run << 1 | grp) : run8;  // gate and up runs alternate: rows r and r + 16 pair up
       const uint32_t row = ((k >> 3) * 2 + (slot >> 2)) * 1024 + (k & 7) * 128;
       const int c = (slot & 3) * 2;
       a_off[j][0] = row + ((c ^ (k & 7)) << 4);
       a_off[j][1] = row + (((c + 1) ^ (k & 7)) << 4);
     }
-    Ring rr, ra;
-    for (int i = 0; i < n_steps; ++i, ra.next(SA)) {
-      const int r = rr.slot, sa = ra.slot;
-      if (i % STAGE_STEPS == 0) mbar_wait(smem_u32(raw_full + r), rr.phase, abort_flag, WAIT_RAW_FULL);
-      mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
-      const uint8_t* raw = sRaw + r * RAW_STAGE + (i % STAGE_STEPS) * UNIT;
-      uint8_t* slot = sA + sa * A_SLOT_BYTES;
+    using RawT = typename std::conditional<FMT == FB_BFP8, uint4, uint2>::type;
+    RawT q[AHEAD][2];
+    uint32_t top[AHEAD][2];
+    const int units_here = units_total - s0 * STEP_UNITS;  // units of K from this CTA's first step to the end of K
+    auto fetch = [&](int step, int buf) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const uint2 sc2 = lut[raw[exp_off[j]]];
-        const Scale8 sc{sc2.x, sc2.y};
-        uint32_t v[8];
-        if (FMT == FB_BFP8) {
-          const uint4 q = *reinterpret_cast<const uint4*>(raw + raw_off[j]);
-          unpack8_word(q.x, sc, v[0], v[1]);
-          unpack8_word(q.y, sc, v[2], v[3]);
-          unpack8_word(q.z, sc, v[4], v[5]);
-          unpack8_word(q.w, sc, v[6], v[7]);
-        } else {
-          const uint2 q = *reinterpret_cast<const uint2*>(raw + raw_off[j]);
-          unpack4_word(q.x, sc, v);
-          unpack4_word(q.y, sc, v + 4);
+        const bool ok = col_ok[j] && step < n_steps && step * STEP_UNITS + unit_of[j] < units_here;
+        const uint8_t* at = src[j] + (int64_t)step * (STEP_UNITS * UNIT);
+        if (ok) {
+          q[buf][j] = __ldg(reinterpret_cast<const RawT*>(at));
+          top[buf][j] = __ldg(at + exp_rel[j]);
+        } else {  // past the end of K, or a column group past N: zeros
+          q[buf][j] = RawT{};
+          if (FMT == FB_BFP4) q[buf][j].x = 0x88888888u, q[buf][j].y = 0x88888888u;
+          top[buf][j] = 0;
         }
-        *reinterpret_cast<uint4*>(slot + a_off[j][0]) = make_uint4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<uint4*>(slot + a_off[j][1]) = make_uint4(v[4], v[5], v[6], v[7]);
       }
-      fence_proxy_async();
-      __syncwarp();
-      const bool stage_done = i % STAGE_STEPS == STAGE_STEPS - 1 || i == n_steps - 1;
-      if (lane == 0) {
-        if (stage_done) mbar_arrive(smem_u32(raw_empty + r));
-        mbar_arrive(smem_u32(a_full + sa));
+    };
+#pragma unroll
+    for (int d = 0; d < AHEAD; ++d) fetch(d, d);
+    const uint32_t sA32 = smem_u32(sA), lut32 = smem_u32(lut);
+    Ring ra;
+    for (int i0 = 0; i0 < n_steps; i0 += AHEAD) {
+#pragma unroll
+      for (int d = 0; d < AHEAD; ++d) {  // (buffers indexed by constants: they stay in registers)
+        const int i = i0 + d;
+        if (i < n_steps) {
+          const int sa = ra.slot;
+          mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
+          const uint32_t slot = sA32 + sa * A_SLOT_BYTES;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint2 sc2 = ld_shared_v2(lut32 + top[d][j] * 8);
+            const Scale8 sc{sc2.x, sc2.y};
+            uint32_t v[8];
+            if constexpr (FMT == FB_BFP8) {
+              unpack8_word(q[d][j].x, sc, v[0], v[1]);
+              unpack8_word(q[d][j].y, sc, v[2], v[3]);
+              unpack8_word(q[d][j].z, sc, v[4], v[5]);
+              unpack8_word(q[d][j].w, sc, v[6], v[7]);
+            } else {
+              unpack4_word(q[d][j].x, sc, v);
+              unpack4_word(q[d][j].y, sc, v + 4);
+            }
+            st_shared_v4(slot + a_off[j][0], v[0], v[1], v[2], v[3]);
+            st_shared_v4(slot + a_off[j][1], v[4], v[5], v[6], v[7]);
+          }
+          fetch(i + AHEAD, d);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+          ra.next(SA);
+        }
       }
-      if (stage_done) rr.next(R);
     }
   }
 
   // ---- accumulators -> the owning CTA's shared memory.  CTA `rank` of the cluster (= its K split) owns rows
   // [rank * rows_per, (rank + 1) * rows_per) of the tile; exchange[src][t][row] is what CTA src summed for them.
   const bool worker = warp < WORKERS / 32;
-  const int splits = p.splits, rows_per = TILE_N / splits;
+  const int splits = p.splits, rows_per = (TILE_N + splits - 1) / splits;  // (the last rank may own fewer rows)
   float* exchange = reinterpret_cast<float*>(sA);
   if (worker) {
     mbar_wait(smem_u32(acc_full), 0, abort_flag, WAIT_ACC);
@@ -212,8 +235,9 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   }
   if (splits > 1) cluster_sync();  // every CTA of the cluster is past its MMAs: the A slots are free to receive
   else __syncthreads();
-  if (worker) {
-    const int q = warp & 3, ncol = nt / 2, col0 = (warp >> 2) * ncol, row = 32 * q + lane;
+  const int col_groups = nt >= 32 ? 4 : nt / 8;  // worker warps sharing one quarter of the TMEM lanes split the token columns
+  if (worker && (warp >> 2) < col_groups) {
+    const int q = warp & 3, ncol = nt / col_groups, col0 = (warp >> 2) * ncol, row = 32 * q + lane;
     const uint32_t owner = row / rows_per;
     const uint32_t at = smem_u32(exchange) + (uint32_t)(((split * nt + col0) * rows_per + row % rows_per) * 4);
     for (int cb = 0; cb < ncol; cb += 8) {
@@ -234,31 +258,47 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   // ---- epilogue over this CTA's rows: sum the splits in rank order, scale, SwiGLU / residual, store
   if (worker) {
     const int64_t M = a.M;
-    const int out_rows = swiglu ? rows_per / 2 : rows_per;  // SwiGLU: rows 32q..32q+15 are gates, the next 16 their ups
-    for (int idx = tid; idx < out_rows * nt; idx += WORKERS) {
-      const int t = idx / out_rows, o = idx % out_rows;
-      if (t >= M) break;
-      const int lr = swiglu ? (o / 16) * 32 + o % 16 : o;  // row inside this CTA's slice
-      float val = 0.f, up = 0.f;
-      for (int s = 0; s < splits; ++s) {
-        const float* src = exchange + ((size_t)s * nt + t) * rows_per;
-        val += src[lr];
-        if (swiglu) up += src[lr + 16];
+    const int own = min(rows_per, TILE_N - split * rows_per);   // rows of the tile this CTA owns
+    const int out_rows = swiglu ? own / 2 : own;  // SwiGLU: rows 32q..32q+15 are gates, the next 16 their ups
+    const int total = out_rows * (int)min((int64_t)nt, M);
+    for (int base = tid; base < total; base += 4 * WORKERS) {
+      float res[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {  // the residual reads of four outputs are in flight together
+        const int idx = base + e * WORKERS;
+        res[e] = 0.f;
+        if (idx < total && a.epilogue == FB_EPI_RESIDUAL) {
+          const int t = idx / out_rows, n = TILE_N * tile + split * rows_per + idx % out_rows;
+          if (n < a.N) res[e] = bf16_bits_to_float(__ldg(static_cast<const uint16_t*>(a.residual) + t * a.ldr + n));
+        }
       }
-      if (p.rstd) val *= p.rstd[t], up *= p.rstd[t];
-      const int tr = split * rows_per + lr;  // row inside the tile
-      int64_t n;
-      if (swiglu) {
-        val = val / (1.f + __expf(-val)) * up;
-        n = 64 * (int64_t)tile + (tr / 32) * 16 + tr % 16;
-        if (n >= a.N / 2) continue;
-      } else {
-        n = TILE_N * (int64_t)tile + tr;
-        if (n >= a.N) continue;
-        if (a.epilogue == FB_EPI_RESIDUAL) val += bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[t * a.ldr + n]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int idx = base + e * WORKERS;
+        if (idx >= total) break;
+        const int t = idx / out_rows, o = idx % out_rows;
+        const int lr = swiglu ? (o / 16) * 32 + o % 16 : o;  // row inside this CTA's slice
+        float val = 0.f, up = 0.f;
+        for (int s = 0; s < splits; ++s) {
+          const float* src = exchange + ((size_t)s * nt + t) * rows_per;
+          val += src[lr];
+          if (swiglu) up += src[lr + 16];
+        }
+        if (p.rstd) val *= p.rstd[t], up *= p.rstd[t];
+        const int tr = split * rows_per + lr;  // row inside the tile
+        int64_t n;
+        if (swiglu) {
+          val = val / (1.f + __expf(-val)) * up;
+          n = 64 * (int64_t)tile + (tr / 32) * 16 + tr % 16;
+          if (n >= a.N / 2) continue;
+        } else {
+          n = TILE_N * (int64_t)tile + tr;
+          if (n >= a.N) continue;
+          val += res[e];
+        }
+        if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[t * a.ldo + n] = val;
+        else static_cast<uint16_t*>(a.out)[t * a.ldo + n] = (uint16_t)float_to_bf16_bits(val);
       }
-      if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[t * a.ldo + n] = val;
-      else static_cast<uint16_t*>(a.out)[t * a.ldo + n] = (uint16_t)float_to_bf16_bits(val);
     }
   }
   __syncthreads();
@@ -306,7 +346,7 @@ EncodeTiled encode_tiled() {
 }
 
 struct Plan {
-  int nt, tmem_cols, tiles, splits, sps, steps, raw_stages, x_slots, a_slots;
+  int nt, tmem_cols, tiles, splits, sps, steps, x_slots, a_slots;
   size_t smem;
 };
 
@@ -315,26 +355,24 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue) {
   pl.nt = (int)((M + 15) / 16 * 16);
   pl.tmem_cols = pl.nt <= 32 ? 32 : pl.nt <= 64 ? 64 : 128;
   pl.tiles = (int)(epilogue == FB_EPI_SWIGLU ? groups_of(N) / 2 : (groups_of(N) + 1) / 2);
-  pl.steps = (int)ksteps_of(K);
-  const bool two_per_sm = pl.nt <= 32;
-  int want = (two_per_sm ? 296 : 148) / pl.tiles;  // CTAs that can be resident at once
-  int most = pl.steps / 4 < 1 ? 1 : pl.steps / 4;  // at least 256 rows of K per CTA
-  int splits = want < most ? want : most;
-  const int cap = epilogue == FB_EPI_SWIGLU ? 4 : 8;  // a cluster's CTAs; SwiGLU's row pairs stay inside a 32-row slice
-  splits = splits > cap ? cap : splits < 1 ? 1 : splits;
-  while (splits & (splits - 1)) --splits;  // a power of two divides the tile's 128 rows
-  pl.sps = (int)ceil_div(pl.steps, splits);
-  while (splits > 1 && (int)ceil_div(pl.steps, pl.sps) < splits) splits >>= 1, pl.sps = (int)ceil_div(pl.steps, splits);
-  pl.splits = splits;
-  const int raw = 2 * STAGE_STEPS * unit_bytes(fmt);
-  pl.x_slots = 4;
-  pl.a_slots = two_per_sm ? 3 : 4;
-  if (pl.a_slots * A_SLOT_BYTES < TILE_N * pl.nt * 4) pl.a_slots = 4;  // room for the split-K exchange
-  const size_t fixed = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * pl.nt * 128 + 2048 + 7 * MAX_STAGES * 8 + 64;
-  const size_t budget = two_per_sm ? 113 * 1024 : 220 * 1024;
-  int stages = (int)((budget - fixed) / raw);
-  pl.raw_stages = stages > MAX_STAGES ? MAX_STAGES : stages;
-  pl.smem = fixed + (size_t)pl.raw_stages * raw;
+  pl.steps = (int)ceil_div(K, STEP_ROWS);
+  // K splits (a cluster of up to 8 CTAs per tile): the count with the least modelled time, waves x (a CTA's fixed
+  // cost + its steps); SwiGLU's gate/up row pairs must stay inside one CTA's slice of rows
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 8; ++s) {
+    if (s > 1 && pl.steps / s < 2) break;
+    if (epilogue == FB_EPI_SWIGLU && s != 1 && s != 2 && s != 4) continue;
+    const int per = (int)ceil_div(pl.steps, s);
+    if ((int)ceil_div(pl.steps, per) != s) continue;  // every split gets work
+    const double cost = (double)ceil_div((int64_t)pl.tiles * s, 148) * (5.0 + (s > 1 ? 1.0 : 0.0) + 0.6 * per);
+    if (cost < best_cost) best_cost = cost, best = s;
+  }
+  pl.splits = best;
+  pl.sps = (int)ceil_div(pl.steps, best);
+  pl.a_slots = pl.nt <= 64 ? 4 : 3;
+  pl.x_slots = pl.nt <= 64 ? 4 : 3;
+  pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 2048 + 5 * MAX_STAGES * 8 + 64;
   return pl;
 }
 
@@ -356,7 +394,7 @@ static int run_pass(const LinearArgs& a, cudaStream_t s) {
   GemmParams p{};
   p.a = a;
   p.nt = pl.nt, p.tmem_cols = pl.tmem_cols, p.splits = pl.splits, p.steps_per_split = pl.sps, p.steps_total = pl.steps;
-  p.raw_stages = pl.raw_stages, p.x_slots = pl.x_slots, p.a_slots = pl.a_slots;
+  p.x_slots = pl.x_slots, p.a_slots = pl.a_slots;
   const void* x = a.x;
   int64_t ldx = a.ldx;
   if (a.norm_w) {
@@ -374,7 +412,7 @@ static int run_pass(const LinearArgs& a, cudaStream_t s) {
   CUtensorMap tmap;
   const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
   const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-  const cuuint32_t box[2] = {KSTEP, (cuuint32_t)pl.nt}, estr[2] = {1, 1};
+  const cuuint32_t box[2] = {KSTEP, (cuuint32_t)pl.nt}, estr[2] = {1, 1};  // 64 bf16 = one 128-byte swizzled row per token
   CUresult rc = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -95,3 +95,63 @@ def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="no
                           out.stride(0), _ptr(norm_w), eps, epi, _ptr(residual), residual.stride(0) if residual is not None else 0,
                           _ptr(workspace), workspace.numel() if workspace is not None else 0, _stream()))
     return out
+
+
+def gather_rows(table, ids, out=None):
+    """table[ids] for a 2-D table and an int32 vector of ids on the device (Tensor.gather)."""
+    assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32 and ids.dim() == 1
+    if out is None:
+        out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    check(lib().fb_gather_rows(table.data_ptr(), table.shape[0], table.shape[1] * table.element_size(), ids.data_ptr(), ids.numel(),
+                               out.data_ptr(), _stream()))
+    return out
+
+
+def rope_kv_write(qkv, cos, sin, places, rows, cache, H, KV, hd, q_out=None, qk_norm=None, eps=1e-5):
+    """RoPE (and Qwen3's q/k norm) on a fused qkv [T, (H+2KV)*hd]; q -> q_out [T, H*hd], k and v into cache
+    [2*KV, cache_rows, hd] at rows."""
+    T = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.shape[1] == (H + 2 * KV) * hd and qkv.stride(1) == 1
+    assert cache.dtype == torch.bfloat16 and cache.shape[0] == 2 * KV and cache.shape[2] == hd and cache.is_contiguous()
+    assert places.dtype == torch.int32 and rows.dtype == torch.int32 and places.numel() == T and rows.numel() == T
+    assert cos.shape == sin.shape and cos.is_contiguous() and sin.is_contiguous() and cos.dtype == torch.bfloat16
+    if q_out is None:
+        q_out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=qkv.device)
+    check(lib().fb_rope_kv_write(qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1], places.data_ptr(),
+                                 rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0), cache.data_ptr(), cache.shape[1], _stream()))
+    return q_out
+
+
+_ATT_WS = {}
+
+
+def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=None):
+    """One token per sequence: token t attends cache rows base[t] .. base[t] + place[t] of its kv head."""
+    T = q.shape[0]
+    assert q.dtype == torch.bfloat16 and q.shape[1] == H * hd and q.stride(1) == 1 and cache.is_contiguous()
+    assert base.dtype == torch.int32 and place.dtype == torch.int32 and base.numel() == T and place.numel() == T
+    if out is None:
+        out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=q.device)
+    need = lib().fb_decode_attention_workspace_bytes(T, H, KV, hd, max_keys)
+    ws = _ATT_WS.get(q.device)
+    if need and (ws is None or ws.numel() < need):
+        ws = _ATT_WS[q.device] = torch.empty(need, dtype=torch.uint8, device=q.device)
+    check(lib().fb_decode_attention(q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data_ptr(), cache.shape[1], base.data_ptr(), place.data_ptr(),
+                                    max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None, ws.numel() if need else 0, _stream()))
+    return out
+
+
+def rmsnorm(x, w, eps=1e-5, out=None):
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and w.numel() == x.shape[1]
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib().fb_rmsnorm(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), w.data_ptr(), eps, out.data_ptr(), out.stride(0), _stream()))
+    return out
+
+
+def argmax(logits, out=None):
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    check(lib().fb_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), out.data_ptr(), _stream()))
+    return out

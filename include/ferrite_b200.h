@@ -100,6 +100,42 @@ int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const v
               int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,
               int64_t ldr, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- the rest of a decode step ------------------------------------------------------------------------- */
+
+/* out[i, :] = table[ids[i], :]: Tensor.gather, the embedding lookup (ferrite/tensor.py:116-126,
+ * ferrite/compiler.py:1574-1580).  ids are read on the device; rows of row_bytes bytes (a multiple of 16). */
+int fb_gather_rows(const void* table, int64_t table_rows, int64_t row_bytes, const int32_t* ids, int64_t n, void* out,
+                   void* stream);
+
+/* After the fused qkv matmul (models/llama.py:111-128): per head optional RMSNorm of q and k heads by
+ * qk_norm[(H+KV)*hd] (Qwen3, llama.py:121-123), RoPE in Hugging Face's half-rotation form with bf16 tables
+ * (llama.py:92-93, 351-368), then q heads -> q_out[T, H*hd] and the k and v heads into the cache rows
+ * (Tensor.put, ferrite/tensor.py:128-140; ferrite/compiler.py:1638-1650): cache[(k heads, v heads)][rows[t]][:],
+ * cache laid out [2*KV, cache_rows, hd] as models/llama.py:506-514.  cos / sin: [places, table_cols] with
+ * table_cols = hd (one head's table) or (H + 2*KV)*hd (ferrite's, v's columns 1 and 0).  places[t] picks the
+ * table row, rows[t] the cache row (place + the sequence's first row, llama.py:443-445). */
+int fb_rope_kv_write(const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos, const void* sin,
+                     int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps,
+                     void* q_out, int64_t ld_q, void* cache, int64_t cache_rows, void* stream);
+
+/* softmax(q k^T / sqrt(hd) + mask) v over the bf16 KV cache for one token per sequence: Tensor.attend
+ * (ferrite/tensor.py:487-516, ferrite/compiler.py:1147-1170) as models/llama.py:129-146 uses it.  Token t reads
+ * cache rows base[t] .. base[t] + place[t] of its kv head (with window > 0 only the last `window` of them);
+ * its H/KV query heads share every key row read.  max_keys: an upper bound of place[t] + 1 (it sizes the split
+ * of the keys across CTAs, flash-decoding; ferrite's `parts`).  hd is 64 or 128; H/KV <= 16.
+ * workspace: fb_decode_attention_workspace_bytes(...) bytes (partial sums of the key splits). */
+size_t fb_decode_attention_workspace_bytes(int64_t T, int H, int KV, int hd, int64_t max_keys);
+int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
+                        const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* x * rsqrt(mean(x^2) + eps) * w, row by row (models/llama.py:82-85), bf16 in and out */
+int fb_rmsnorm(const void* x, int64_t rows, int64_t cols, int64_t ldx, const void* w, float eps, void* out, int64_t ldo,
+               void* stream);
+
+/* greedy pick: each row's first largest fp32 logit (what models/llama.py:787-795 does on the host with argmax) */
+int fb_argmax(const void* logits_f32, int64_t rows, int64_t cols, int64_t ld, int32_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

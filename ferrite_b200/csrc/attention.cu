@@ -15,19 +15,25 @@
 
 namespace fb {
 
+// One CTA serves one ENTRY: up to 16 query rows that share one run of keys (a kv head's query heads for a token; or
+// 16 tokens of one head in a prefill).  Entries are numbered e = e0 * E1 + e1 and every operand is addressed by
+// two-level strides (in elements), so both the token-major order of a fused decode step and ferrite's
+// (kv head, sequence) batch order (models/llama.py:132-135) are read in place.
 struct AttnArgs {
-  const uint16_t* q;  // [T, H * hd]
-  int64_t ld_q;
-  const uint16_t* cache;  // [2 KV, cache_rows, hd]: keys' heads then values'
-  int64_t cache_rows;
-  const int32_t *base, *place;  // [T]
+  const uint16_t* q;  // row r of entry e at q + e0*q_s0 + e1*q_s1 + r*q_sr
+  int64_t q_s0, q_s1, q_sr;
+  const uint16_t *k, *v;  // key j of entry e at k + e0*kv_s0 + e1*kv_s1 + (base[e0] + j)*hd
+  int64_t kv_s0, kv_s1;
+  const int32_t* base;   // [E0] first cache row of a sequence, or null
+  const int32_t* place;  // row r of entry e sees keys 0..place[e0*p_s0 + e1*p_s1 + r*p_sr]
+  int64_t p_s0, p_s1, p_sr;
+  int E1, rows;  // rows per entry
   int window;
-  int H, KV;
-  float scale_log2;  // log2(e) / sqrt(hd)
-  uint16_t* out;     // [T, H * hd]
-  int64_t ld_o;
-  float* part_o;   // [T * KV, splits, 16, hd]
-  float* part_ml;  // [T * KV, splits, 16, 2]
+  float scale_log2;  // log2(e) * scale of the scores
+  uint16_t* out;     // like q
+  int64_t o_s0, o_s1, o_sr;
+  float* part_o;   // [entries * row tiles, splits, 16, hd]
+  float* part_ml;  // [entries * row tiles, splits, 16, 2]
   int splits;
 };
 
@@ -65,17 +71,32 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
   uint8_t* sK = sQ + 16 * HD * 2;          // 2 x [64][HD]
   uint8_t* sV = sK + 2 * TILE_BYTES;       // 2 x [64][HD]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t = blockIdx.x / a.KV, g = blockIdx.x % a.KV, split = blockIdx.y;
-  const int rep = a.H / a.KV;
+  const int e = blockIdx.x, e0 = e / a.E1, e1 = e % a.E1, split = blockIdx.y, row0 = blockIdx.z * 16;
+  const int rep = min(16, a.rows - row0);  // rows of this tile
 
-  // the keys this CTA reads: the token's visible range, cut into `splits` runs of whole tiles
-  const int len = a.place[t] + 1;
-  const int first = a.window > 0 ? max(0, len - a.window) : 0;
+  // the keys this CTA reads: what its rows can see, cut into `splits` runs of whole tiles
+  const int32_t* places = a.place + e0 * a.p_s0 + e1 * a.p_s1 + (int64_t)row0 * a.p_sr;
+  int len = 0, least = 0x7fffffff;
+  for (int r = 0; r < rep; ++r) {
+    const int p = places[r * a.p_sr];
+    len = max(len, p + 1), least = min(least, p);
+  }
+  const int first = a.window > 0 ? max(0, least + 1 - a.window) : 0;
   const int per = ((len - first + a.splits - 1) / a.splits + KEY_TILE - 1) / KEY_TILE * KEY_TILE;
   const int k0 = first + split * per, k1 = min(len, k0 + per);
   const int n_tiles = k1 > k0 ? (k1 - k0 + KEY_TILE - 1) / KEY_TILE : 0;
-  const uint16_t* Kg = a.cache + ((int64_t)g * a.cache_rows + a.base[t]) * HD;
-  const uint16_t* Vg = a.cache + ((int64_t)(a.KV + g) * a.cache_rows + a.base[t]) * HD;
+  const int64_t kv_off = e0 * a.kv_s0 + e1 * a.kv_s1 + (a.base ? (int64_t)a.base[e0] * HD : 0);
+  const uint16_t* Kg = a.k + kv_off;
+  const uint16_t* Vg = a.v + kv_off;
+  const uint16_t* Qg = a.q + e0 * a.q_s0 + e1 * a.q_s1 + (int64_t)row0 * a.q_sr;
+  // this thread's two rows (lane/4 and lane/4 + 8) see keys window_lo .. place
+  int place_r[2], lo_r[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + 8 * h;
+    place_r[h] = r < rep ? places[r * a.p_sr] : -1;
+    lo_r[h] = a.window > 0 ? place_r[h] + 1 - a.window : 0;
+  }
 
   auto load_tile = [&](int i, int buf) {
     const int key0 = k0 + i * KEY_TILE;
@@ -93,7 +114,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
   for (int c = tid; c < 16 * CH; c += ATT_THREADS) {
     const int r = c / CH, ch = c % CH;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rep) v = *reinterpret_cast<const uint4*>(a.q + t * a.ld_q + (int64_t)(g * rep + r) * HD + ch * 8);
+    if (r < rep) v = *reinterpret_cast<const uint4*>(Qg + r * a.q_sr + ch * 8);
     *reinterpret_cast<uint4*>(sQ + tile_off<HD>(r, ch)) = v;
   }
   __syncthreads();
@@ -132,9 +153,10 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
+      for (int e = 0; e < 4; ++e) {  // (e: the accumulator's element, not the entry)
         const int key = key_first + nt * 8 + (e & 1);
-        s[nt][e] = key < k1 ? s[nt][e] * a.scale_log2 : -INFINITY;
+        const bool seen = key < k1 && key <= place_r[e >> 1] && key >= lo_r[e >> 1];
+        s[nt][e] = seen ? s[nt][e] * a.scale_log2 : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
     float corr[2];
@@ -205,21 +227,21 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
       acc += so[(w * 16 + r) * HD + d] * f;
     }
     if (a.splits == 1) {
-      a.out[t * a.ld_o + (int64_t)(g * rep + r) * HD + d] = (uint16_t)float_to_bf16_bits(l > 0.f ? acc / l : 0.f);
+      a.out[e0 * a.o_s0 + e1 * a.o_s1 + (int64_t)(row0 + r) * a.o_sr + d] = (uint16_t)float_to_bf16_bits(l > 0.f ? acc / l : 0.f);
     } else {
-      const int64_t at = ((int64_t)blockIdx.x * a.splits + split) * 16 + r;
+      const int64_t at = (((int64_t)blockIdx.x * gridDim.z + blockIdx.z) * a.splits + split) * 16 + r;
       a.part_o[at * HD + d] = acc;
       if (d == 0) a.part_ml[at * 2] = m, a.part_ml[at * 2 + 1] = l;
     }
   }
 }
 
-// one block per (token, query head): weight each split by exp2(its max - the overall max), sum, divide
+// one block per (entry, row): weight each split by exp2(its max - the overall max), sum, divide
 template <int HD>
 __global__ void __launch_bounds__(HD) attention_combine_kernel(AttnArgs a) {
-  const int t = blockIdx.x / a.H, h = blockIdx.x % a.H, d = threadIdx.x;
-  const int rep = a.H / a.KV, g = h / rep, r = h % rep;
-  const int64_t first = ((int64_t)(t * a.KV + g) * a.splits) * 16 + r;
+  const int e = blockIdx.x / a.rows, row = blockIdx.x % a.rows, d = threadIdx.x;
+  const int e0 = e / a.E1, e1 = e % a.E1, tiles = (a.rows + 15) / 16;
+  const int64_t first = (((int64_t)e * tiles + row / 16) * a.splits) * 16 + row % 16;
   float m = -INFINITY;
   for (int s = 0; s < a.splits; ++s) m = fmaxf(m, a.part_ml[(first + s * 16) * 2]);
   const float m_safe = m == -INFINITY ? 0.f : m;
@@ -229,56 +251,94 @@ __global__ void __launch_bounds__(HD) attention_combine_kernel(AttnArgs a) {
     l += a.part_ml[(first + s * 16) * 2 + 1] * f;
     acc += a.part_o[(first + s * 16) * HD + d] * f;
   }
-  a.out[t * a.ld_o + (int64_t)h * HD + d] = (uint16_t)float_to_bf16_bits(l > 0.f ? acc / l : 0.f);
+  a.out[e0 * a.o_s0 + e1 * a.o_s1 + (int64_t)row * a.o_sr + d] = (uint16_t)float_to_bf16_bits(l > 0.f ? acc / l : 0.f);
 }
 
-static int pick_splits(int64_t T, int KV, int64_t max_keys) {
-  const int64_t ctas = T * KV;
-  int64_t want = (4 * 148 + ctas - 1) / ctas;               // about four CTAs per SM in flight
+static int pick_splits(int64_t ctas, int64_t max_keys) {
+  int64_t want = (4 * 148 + ctas - 1) / ctas;                           // about four CTAs per SM in flight
   const int64_t most = (max_keys + 2 * KEY_TILE - 1) / (2 * KEY_TILE);  // at least two tiles per split
   want = want > most ? most : want;
   return (int)(want < 1 ? 1 : want > 32 ? 32 : want);
 }
 
+static size_t attention_workspace(int64_t entries, int rows, int hd, int64_t max_keys, int* splits_out) {
+  const int64_t ctas = entries * ((rows + 15) / 16);
+  const int splits = pick_splits(ctas, max_keys);
+  if (splits_out) *splits_out = splits;
+  return splits == 1 ? 0 : (size_t)ctas * splits * 16 * (hd + 2) * sizeof(float);
+}
+
+static int launch_attention(AttnArgs a, int64_t entries, int hd, int64_t max_keys, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+  int splits;
+  const size_t need = attention_workspace(entries, a.rows, hd, max_keys, &splits);
+  if (need && (!workspace || workspace_bytes < need)) {
+    set_error("attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return FB_ERR_MEMORY;
+  }
+  const int tiles = (a.rows + 15) / 16;
+  a.splits = splits;
+  a.part_o = (float*)workspace;
+  a.part_ml = (float*)workspace + (size_t)entries * tiles * splits * 16 * hd;
+  dim3 grid((unsigned)entries, (unsigned)splits, (unsigned)tiles);
+  const size_t smem = (size_t)(16 + 4 * KEY_TILE) * hd * 2;
+  if (hd == 128) {
+    static bool once = false;
+    if (!once) cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
+    decode_attention_kernel<128><<<grid, ATT_THREADS, smem, s>>>(a);
+    if (splits > 1) attention_combine_kernel<128><<<(unsigned)(entries * a.rows), 128, 0, s>>>(a);
+  } else {
+    static bool once = false;
+    if (!once) cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
+    decode_attention_kernel<64><<<grid, ATT_THREADS, smem, s>>>(a);
+    if (splits > 1) attention_combine_kernel<64><<<(unsigned)(entries * a.rows), 64, 0, s>>>(a);
+  }
+  return launch_status("attention");
+}
+
 }  // namespace fb
 
 extern "C" size_t fb_decode_attention_workspace_bytes(int64_t T, int H, int KV, int hd, int64_t max_keys) {
-  (void)H;
-  const int splits = fb::pick_splits(T, KV, max_keys);
-  return splits == 1 ? 0 : (size_t)T * KV * splits * 16 * (hd + 2) * sizeof(float);
+  return fb::attention_workspace(T * KV, H / KV, hd, max_keys, nullptr);
 }
 
 extern "C" int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
-                                   const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
+                                   int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
                                    void* workspace, size_t workspace_bytes, void* stream) {
   FB_REQUIRE(q && cache && base && place && out && T >= 1, "fb_decode_attention: null pointer or no tokens");
   FB_REQUIRE(hd == 64 || hd == 128, "fb_decode_attention: heads of 64 or 128 columns (got %d)", hd);
   FB_REQUIRE(KV >= 1 && H % KV == 0 && H / KV <= 16, "fb_decode_attention: up to 16 query heads per key head (got %d / %d)", H, KV);
   FB_REQUIRE(ld_q >= (int64_t)H * hd && ld_o >= (int64_t)H * hd && ld_q % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)cache % 16 == 0,
              "fb_decode_attention: rows of q 16-byte aligned");
-  FB_REQUIRE(max_keys >= 1 && max_keys <= cache_rows && window >= 0, "fb_decode_attention: max_keys within the cache");
-  const int splits = fb::pick_splits(T, KV, max_keys);
-  const size_t need = splits == 1 ? 0 : (size_t)T * KV * splits * 16 * (hd + 2) * sizeof(float);
-  if (need && (!workspace || workspace_bytes < need)) {
-    fb::set_error("fb_decode_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
-    return FB_ERR_MEMORY;
-  }
-  fb::AttnArgs a{(const uint16_t*)q, ld_q, (const uint16_t*)cache, cache_rows, base, place, window, H, KV,
-                 1.4426950408889634f / sqrtf((float)hd), (uint16_t*)out, ld_o, (float*)workspace,
-                 (float*)workspace + (size_t)T * KV * splits * 16 * hd, splits};
-  auto s = (cudaStream_t)stream;
-  dim3 grid((unsigned)(T * KV), (unsigned)splits);
-  const size_t smem = (size_t)(16 + 4 * fb::KEY_TILE) * hd * 2;
-  if (hd == 128) {
-    static bool once = false;
-    if (!once) cudaFuncSetAttribute(fb::decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
-    fb::decode_attention_kernel<128><<<grid, fb::ATT_THREADS, smem, s>>>(a);
-    if (splits > 1) fb::attention_combine_kernel<128><<<(unsigned)(T * H), 128, 0, s>>>(a);
-  } else {
-    static bool once = false;
-    if (!once) cudaFuncSetAttribute(fb::decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
-    fb::decode_attention_kernel<64><<<grid, fb::ATT_THREADS, smem, s>>>(a);
-    if (splits > 1) fb::attention_combine_kernel<64><<<(unsigned)(T * H), 64, 0, s>>>(a);
-  }
-  return fb::launch_status("fb_decode_attention");
+  FB_REQUIRE(max_keys >= 1 && max_keys <= cache_rows && window >= 0 && cache_head_stride >= cache_rows * hd, "fb_decode_attention: max_keys within the cache");
+  const int rep = H / KV;
+  fb::AttnArgs a{};
+  a.q = (const uint16_t*)q, a.q_s0 = ld_q, a.q_s1 = (int64_t)rep * hd, a.q_sr = hd;  // entry (token, kv head): its rep query heads
+  a.k = (const uint16_t*)cache, a.v = (const uint16_t*)cache + (int64_t)KV * cache_head_stride;
+  a.kv_s0 = 0, a.kv_s1 = cache_head_stride, a.base = base;
+  a.place = place, a.p_s0 = 1, a.p_s1 = 0, a.p_sr = 0;
+  a.E1 = KV, a.rows = rep, a.window = window, a.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  a.out = (uint16_t*)out, a.o_s0 = ld_o, a.o_s1 = (int64_t)rep * hd, a.o_sr = hd;
+  return fb::launch_attention(a, T * KV, hd, max_keys, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" size_t fb_attend_workspace_bytes(int64_t entries, int64_t rows, int hd, int64_t max_keys) {
+  return fb::attention_workspace(entries, (int)rows, hd, max_keys, nullptr);
+}
+
+extern "C" int fb_attend(const void* q, int64_t entries, int64_t rows, int hd, int64_t q_entry_stride, int64_t q_row_stride, const void* k,
+                         const void* v, int64_t kv_entry_stride, int64_t kv_rep, int64_t keys, const int32_t* places,
+                         int64_t place_entry_stride, int64_t place_row_stride, int window, float scale, void* out, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  FB_REQUIRE(q && k && v && places && out && entries >= 1 && rows >= 1 && keys >= 1, "fb_attend: null pointer or empty");
+  FB_REQUIRE(hd == 64 || hd == 128, "fb_attend: heads of 64 or 128 columns (got %d)", hd);
+  FB_REQUIRE(kv_rep >= 1 && q_row_stride % 8 == 0 && q_entry_stride % 8 == 0 && kv_entry_stride % 8 == 0 && (uintptr_t)q % 16 == 0 &&
+                 (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0,
+             "fb_attend: rows 16-byte aligned");
+  fb::AttnArgs a{};
+  a.q = (const uint16_t*)q, a.q_s0 = q_entry_stride * kv_rep, a.q_s1 = q_entry_stride, a.q_sr = q_row_stride;
+  a.k = (const uint16_t*)k, a.v = (const uint16_t*)v, a.kv_s0 = kv_entry_stride, a.kv_s1 = 0, a.base = nullptr;  // kv_rep entries share a key matrix
+  a.place = places, a.p_s0 = place_entry_stride * kv_rep, a.p_s1 = place_entry_stride, a.p_sr = place_row_stride;
+  a.E1 = (int)kv_rep, a.rows = (int)rows, a.window = window, a.scale_log2 = 1.4426950408889634f * scale;
+  a.out = (uint16_t*)out, a.o_s0 = rows * hd * kv_rep, a.o_s1 = rows * hd, a.o_sr = hd;
+  return fb::launch_attention(a, entries, hd, keys, workspace, workspace_bytes, (cudaStream_t)stream);
 }

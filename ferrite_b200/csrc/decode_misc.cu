@@ -30,8 +30,8 @@ struct RopeArgs {
   float eps;
   uint16_t* q_out;  // [T, H * hd]
   int64_t ld_q;
-  uint16_t* cache;  // [2 KV, cache_rows, hd]
-  int64_t cache_rows;
+  uint16_t* cache;  // [2 KV, cache_rows, hd], heads head_stride elements apart
+  int64_t head_stride;
   int H, KV, hd;
 };
 
@@ -62,7 +62,7 @@ __global__ void rope_kv_kernel(RopeArgs a) {
   }
   uint16_t* out;
   if (h < a.H) out = a.q_out + t * a.ld_q + (int64_t)h * a.hd;
-  else out = a.cache + ((int64_t)(h - a.H) * a.cache_rows + a.rows[t]) * a.hd;  // k heads, then v heads (models/llama.py:506-514)
+  else out = a.cache + (int64_t)(h - a.H) * a.head_stride + (int64_t)a.rows[t] * a.hd;  // k heads, then v heads (models/llama.py:506-514)
   out[d] = (uint16_t)float_to_bf16_bits(y1);
   out[d + half] = (uint16_t)float_to_bf16_bits(y2);
 }
@@ -117,7 +117,30 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   }
 }
 
+// dst[b, ids[i], :] = src[b, i, :]; of rows with the same place the later one stays (Tensor.put, ferrite/tensor.py:128-140)
+template <typename T>
+__global__ void put_rows_kernel(T* dst, int64_t ds0, int64_t ds1, int64_t ds2, const T* src, int64_t ss0, int64_t ss1, int64_t ss2,
+                                const int32_t* ids, int64_t n, int64_t cols, int64_t dst_rows) {
+  const int64_t i = blockIdx.x, b = blockIdx.y;
+  const int32_t place = ids[i];
+  if (place < 0 || place >= dst_rows) return;
+  for (int64_t j = i + 1; j < n; ++j)
+    if (ids[j] == place) return;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) dst[b * ds0 + place * ds1 + c * ds2] = src[b * ss0 + i * ss1 + c * ss2];
+}
+
 }  // namespace fb
+
+extern "C" int fb_put_rows(void* dst, int64_t ds0, int64_t ds1, int64_t ds2, const void* src, int64_t ss0, int64_t ss1, int64_t ss2,
+                           const int32_t* ids, int64_t batch, int64_t n, int64_t cols, int64_t dst_rows, int elem_bytes, void* stream) {
+  FB_REQUIRE(dst && src && ids && batch >= 1 && n >= 1 && cols >= 1 && batch <= 65535, "fb_put_rows: null pointer or empty");
+  FB_REQUIRE(elem_bytes == 2 || elem_bytes == 4, "fb_put_rows: 2- or 4-byte values");
+  dim3 grid((unsigned)n, (unsigned)batch);
+  auto s = (cudaStream_t)stream;
+  if (elem_bytes == 2) fb::put_rows_kernel<uint16_t><<<grid, 128, 0, s>>>((uint16_t*)dst, ds0, ds1, ds2, (const uint16_t*)src, ss0, ss1, ss2, ids, n, cols, dst_rows);
+  else fb::put_rows_kernel<uint32_t><<<grid, 128, 0, s>>>((uint32_t*)dst, ds0, ds1, ds2, (const uint32_t*)src, ss0, ss1, ss2, ids, n, cols, dst_rows);
+  return fb::launch_status("fb_put_rows");
+}
 
 extern "C" int fb_gather_rows(const void* table, int64_t table_rows, int64_t row_bytes, const int32_t* ids, int64_t n, void* out,
                               void* stream) {
@@ -129,12 +152,13 @@ extern "C" int fb_gather_rows(const void* table, int64_t table_rows, int64_t row
 
 extern "C" int fb_rope_kv_write(const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos, const void* sin,
                                 int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps,
-                                void* q_out, int64_t ld_q, void* cache, int64_t cache_rows, void* stream) {
+                                void* q_out, int64_t ld_q, void* cache, int64_t cache_rows, int64_t cache_head_stride, void* stream) {
   FB_REQUIRE(qkv && cos && sin && places && rows && q_out && cache, "fb_rope_kv_write: null pointer");
   FB_REQUIRE(T >= 1 && H >= 1 && KV >= 1 && hd >= 2 && hd % 2 == 0 && hd <= 512, "fb_rope_kv_write: heads of an even width up to 512");
+  FB_REQUIRE(cache_head_stride >= cache_rows * hd, "fb_rope_kv_write: heads at least cache_rows rows apart");
   FB_REQUIRE(table_cols == hd || table_cols == (int64_t)(H + 2 * KV) * hd, "fb_rope_kv_write: tables one head wide, or as wide as q, k and v");
   fb::RopeArgs a{(const uint16_t*)qkv, ld_qkv, (const uint16_t*)cos, (const uint16_t*)sin, table_cols, places, rows,
-                 (const uint16_t*)qk_norm, eps, (uint16_t*)q_out, ld_q, (uint16_t*)cache, cache_rows, H, KV, hd};
+                 (const uint16_t*)qk_norm, eps, (uint16_t*)q_out, ld_q, (uint16_t*)cache, cache_head_stride, H, KV, hd};
   fb::rope_kv_kernel<<<dim3((unsigned)T, (unsigned)(H + 2 * KV)), hd / 2, 0, (cudaStream_t)stream>>>(a);
   return fb::launch_status("fb_rope_kv_write");
 }

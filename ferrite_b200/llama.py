@@ -1,0 +1,255 @@
+"""A Llama-family decoder on ferrite_b200 Tensors: the layer calls of the reference's models/llama.py (forward, layer,
+attention, mlp, glu, moe, rms, around, kv_cache, precision, weight_format, upload) with the same names, argument meaning
+and weight naming, written for the CUDA backend.
+
+The expressions are the reference's (RMSNorm as x * rsqrt(mean(x*x) + eps) * w, SwiGLU as silu(gate) * up, residual adds);
+the planner in tensor.py fuses them into the block-float matmuls.  Two steps the reference spells as several ops are one
+kernel each here, because their kernels are: RoPE with the KV-cache write (Tensor.rope_put) and attention over the cache
+rows a token's place reaches (Tensor.attend_cache); `around` therefore passes places instead of materialised masks, as
+the reference does on the chip (models/llama.py:450-452)."""
+import math
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+
+from . import ops
+from .tensor import BFP, Tensor, jit  # noqa: F401  (jit re-exported: `from ferrite_b200.llama import jit`)
+
+# a config's fields past a plain Llama's, as a plain Llama has them (models/llama.py:541-543)
+DEFAULTS = dict(head_dim=None, rope=None, sliding=None, k=0, experts=0, moe=0, norm_topk=True, tied=False, precision=None, places=4096,
+                ffn=None, vocab=None, qk_norm=False)
+
+
+def model(**c):
+    return SimpleNamespace(**DEFAULTS | c)
+
+
+def head(c):
+    return c.head_dim or c.dim // c.heads
+
+
+def precision(c, mode="bf16"):
+    """{(op, block): (format, phases)} (models/llama.py:54-76); the phases are kept for the signature and ignored."""
+    four = {"bfp4": ("gate_up",), "experts": ("gate_up", "down")}.get(mode, ())
+    fmt = lambda op: mode if mode in ("bf16", "bfp8") else ("bfp4" if op in four else "bfp8")
+    p = {(op, l): (fmt(op), 4) for l in range(c.layers) for op in ("qkv", "o", "gate_up", "down")}
+    p["head", None] = (fmt("head"), 4)
+    return p
+
+
+def weight_format(name, prec):
+    """A weight's format on the device (models/llama.py:615-623): matmul B operands per `prec`, the rest bf16."""
+    if not prec:
+        return "bf16"
+    if name == "embed.T":
+        return prec.get(("head", None), ("bf16",))[0]
+    if name.startswith("layers.") and name.endswith(("_proj", "experts.gate_up", "experts.down")):
+        op = name.split(".")[-1].removesuffix("_proj")
+        return prec.get((op, int(name.split(".")[1])), ("bf16",))[0]
+    return "bf16"
+
+
+def upload(rt, weights, prec=None):
+    """name -> Tensor from name -> numpy arrays of bf16 values, each cast on the device to its format
+    (models/llama.py:628-640).  qk_norm / qk_on arrive as the reference stacks them ([heads, 1, hd])."""
+    t = {}
+    for name, w in weights.items():
+        a = np.asarray(w, np.float32)
+        a = a.reshape((1,) * (3 - a.ndim) + a.shape) if a.ndim <= 3 else a
+        x = Tensor.of(rt, a)
+        f = weight_format(name, prec)
+        t[name] = x.cast(f).realize() if f != "bf16" else x
+    return t
+
+
+def rms(x, w, c):
+    """RMSNorm scaled by w (models/llama.py:82-85)."""
+    n = x * ((x * x).mean(2) + c.eps).rsqrt()
+    return n * w
+
+
+def glu(gate, up):
+    """SwiGLU's silu(gate) * up (models/llama.py:271-275)."""
+    return gate.silu() * up
+
+
+def mlp(h, p, pre=""):
+    """silu(h @ gate) * (h @ up), then down; gate and up side by side in gate_up_proj (models/llama.py:266-269)."""
+    m = p[pre + "down_proj"].rows
+    gate_up = h.matmul(p[pre + "gate_up_proj"])
+    return glu(gate_up[:, :m], gate_up[:, m:]).matmul(p[pre + "down_proj"])
+
+
+def attention(h, p, c, rotary, seen, cache, rows, slots=None):
+    """A block's attention over its cache (models/llama.py:111-146).  rotary: (cos, sin) tables and the tokens' places;
+    seen: (first cache row of each token's sequence, its last visible key, keys a sequence can hold, window)."""
+    cos, sin, places = rotary
+    base, last, length, window = seen
+    qkv = h.matmul(p["qkv_proj"])
+    q = qkv.rope_put(cos, sin, places, rows, cache, c.heads, c.kv, p.get("qk_norm"), c.eps)
+    o = q.attend_cache(cache, base, last, c.kv, length, window)
+    return o.matmul(p["o_proj"])
+
+
+def moe(h, p, c, live=None):
+    """A mixture of experts in the MLP's place (models/llama.py:277-292): router logits, the k best experts and the
+    softmax of their logits on the device, then every touched expert's SwiGLU for the step's tokens, weighted and summed
+    (the reference's decode form, chip_experts, models/llama.py:302-329)."""
+    logits = h.matmul(p["router"])
+    if c.norm_topk:
+        values, ids = logits.topk(c.k)
+        w = values.softmax()
+    else:
+        w, ids = logits.softmax().topk(c.k)
+    return experts(h, p, ids, w if live is None else w * live)
+
+
+def experts(h, p, ids, w):
+    gate_up, down = p["experts.gate_up"], p["experts.down"]
+    m, e = down.rows, gate_up.batch
+    picks, weights = ids.touched(e, w.bfloat16().realize())
+    x = h.matmul(gate_up, index=picks)
+    g = glu(x[:, :, :m], x[:, :, m:])
+    return (g * weights).matmul(down, index=picks).sum(0)
+
+
+def layer(x, p, c, rotary, seen, cache, rows, live=None, slots=None):
+    """One block: attention then a SwiGLU MLP (or a mixture of experts), each after an RMSNorm and added back
+    (models/llama.py:95-109)."""
+    x = x + attention(rms(x, p["input_layernorm"], c), p, c, rotary, seen, cache, rows, slots)
+    h = rms(x, p["post_attention_layernorm"], c)
+    return x + (moe(h, p, c, live) if "router" in p else mlp(h, p))
+
+
+def firsts(rt, n, slots, part, cache={}):
+    """n tokens' sequences' first rows, n / slots tokens each in turn (models/llama.py:454-457); made once."""
+    key = (id(rt), n, slots, part)
+    if key not in cache:
+        cache[key] = Tensor.of(rt, [[i // (n // slots) * part for i in range(n)]], "int32")
+    return cache[key]
+
+
+def around(w, c, places, size, slots=None, length=None):
+    """For tokens at places: their caches' rows, each one's sequence's first row and last visible key, and which tokens
+    are live (models/llama.py:429-452).  With slots a free slot's token sits on its part's last row: it is not live and
+    sees only its part's first key."""
+    n = places.cols
+    if not slots:
+        zero = firsts(places.rt, n, 1, 0)
+        return places, (zero, places, length or size, getattr(c, "sliding", None) or 0), None
+    part = size // slots
+    base = firsts(places.rt, n, slots, part)
+    rows = (places + base).realize()
+    at = places.reshape(1, n, 1)
+    live = (at < part - 1).bfloat16().realize()
+    last = (places * (places < part - 1)).realize()
+    return rows, (base, last, length or part, getattr(c, "sliding", None) or 0), live
+
+
+def block(w, pre):
+    return {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)}
+
+
+def forward(ids, places, w, c, caches, slots=None, every=False, length=None):
+    """The logits for the token after ids, the tokens at places (models/llama.py:459-480): ids and places int32 row
+    tensors; caches each block's keys' heads then its values'; slots: several sequences decoding together, their caches
+    side by side, the logits every token's."""
+    x = w["embed"].gather(ids)
+    size = caches[0].rows
+    rows, seen, live = around(w, c, places, size, slots, length)
+    rotary = (w["cos"], w["sin"], places)
+    blocks = w.get("_blocks") or [block(w, f"layers.{l}.") for l in range(c.layers)]
+    for l in range(c.layers):
+        x = layer(x, blocks[l], c, rotary, seen, caches[l], rows, live, slots)
+    h = rms(x, w["norm"], c)
+    if not (slots or every):
+        h = h.realize()[:, x.rows - 1:, :]
+    return h.matmul(w["embed.T"], dtype="fp32")
+
+
+def kv_cache(c, size, zeros, slots=1):
+    """Each block's keys' heads then its values', a row for each of size places (models/llama.py:506-514)."""
+    return [zeros((2 * c.kv, size, head(c))) for _ in range(c.layers)]
+
+
+def zeros(rt, dtype="bf16"):
+    """zeros of a shape on the device, for kv_cache (models/llama.py:656-658)."""
+    def make(shape, d=None):
+        t = Tensor(rt, shape[1], shape[2], batch=shape[0], dtype=dtype)
+        t.buf.zero_()
+        return t
+    return make
+
+
+def logits(out):
+    """A row of logits as a numpy vector (models/llama.py:655)."""
+    return out.numpy()[0, 0]
+
+
+def frequencies(c):
+    hd = head(c)
+    inv = 1 / c.theta ** (np.arange(0, hd, 2, dtype=np.float32) / hd)
+    r = c.rope
+    if r and r.get("rope_type") == "llama3":  # Llama 3's scaling of the long wavelengths (models/llama.py:340-345)
+        old, wavelen = r["original_max_position_embeddings"], 2 * math.pi / inv
+        scaled = np.where(wavelen > old / r["low_freq_factor"], inv / r["factor"], inv)
+        smooth = (old / wavelen - r["low_freq_factor"]) / (r["high_freq_factor"] - r["low_freq_factor"])
+        between = (wavelen >= old / r["high_freq_factor"]) & (wavelen <= old / r["low_freq_factor"])
+        inv = np.where(between, (1 - smooth) * scaled / r["factor"] + smooth * scaled, scaled).astype(np.float32)
+    return inv
+
+
+def rotary(c, n, wide=False):
+    """cos and sin for places 0..n-1 as float32 arrays of bf16 values: angles in fp32, tables rounded to bf16
+    (models/llama.py:351-368).  One head's table ([n, hd]; the kernel leaves v's heads unturned), or with wide=True
+    the reference's (one per q, k and v head side by side, v's 1 and 0)."""
+    hd = head(c)
+    angles = np.arange(n, dtype=np.float32)[:, None] * frequencies(c)[None]
+    bf = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).bfloat16().float().numpy()
+    cos, sin = bf(np.concatenate([np.cos(angles)] * 2, 1)), bf(np.concatenate([np.sin(angles)] * 2, 1))
+    if not wide:
+        return cos, sin
+    still = lambda v: np.full((n, hd), v, np.float32)
+    return (np.concatenate([cos] * (c.heads + c.kv) + [still(1)] * c.kv, 1), np.concatenate([sin] * (c.heads + c.kv) + [still(0)] * c.kv, 1))
+
+
+def random_weights(rt, c, prec=None, seed=0, scale=0.02):
+    """Random weights in c's shapes made on the device (for models too large to draw on the host): linear weights
+    N(0, scale) rounded to bf16 then cast to their formats, norm weights 1, RoPE tables for c.places places."""
+    gen = torch.Generator(device=rt.device).manual_seed(seed)
+    hd, d, nh = head(c), c.dim, c.heads + 2 * c.kv
+
+    def draw(name, *shape, sigma=scale):
+        x = torch.empty(*shape, dtype=torch.float32, device=rt.device).normal_(0, sigma, generator=gen).bfloat16()
+        shape3 = (1,) * (3 - len(shape)) + tuple(shape)
+        t = Tensor(rt, shape3[1], shape3[2], batch=shape3[0], buf=x.view(shape3))
+        f = weight_format(name, prec)
+        return t.cast(f).realize() if f != "bf16" else t
+
+    ones = lambda n: Tensor.of(rt, np.ones((1, n), np.float32))
+    w = {}
+    for l in range(c.layers):
+        pre = f"layers.{l}."
+        w[pre + "input_layernorm"], w[pre + "post_attention_layernorm"] = ones(d), ones(d)
+        w[pre + "qkv_proj"] = draw(pre + "qkv_proj", d, nh * hd)
+        w[pre + "o_proj"] = draw(pre + "o_proj", c.heads * hd, d)
+        if c.qk_norm:
+            w[pre + "qk_norm"] = Tensor.of(rt, np.ones((c.heads + c.kv, 1, hd), np.float32))
+        if c.experts:
+            w[pre + "router"] = draw(pre + "router", d, c.experts)
+            w[pre + "experts.gate_up"] = draw(pre + "experts.gate_up", c.experts, d, 2 * c.moe)
+            w[pre + "experts.down"] = draw(pre + "experts.down", c.experts, c.moe, d)
+        else:
+            w[pre + "gate_up_proj"] = draw(pre + "gate_up_proj", d, 2 * c.ffn)
+            w[pre + "down_proj"] = draw(pre + "down_proj", c.ffn, d)
+    w["norm"] = ones(d)
+    embed = torch.empty(c.vocab, d, dtype=torch.float32, device=rt.device).normal_(0, scale, generator=gen).bfloat16()
+    w["embed"] = Tensor(rt, c.vocab, d, buf=embed.view(1, c.vocab, d))
+    et = Tensor(rt, d, c.vocab, buf=embed.t().contiguous().view(1, d, c.vocab))
+    f = weight_format("embed.T", prec)
+    w["embed.T"] = et.cast(f).realize() if f != "bf16" else et
+    cos, sin = rotary(c, c.places)
+    w["cos"], w["sin"] = Tensor.of(rt, cos), Tensor.of(rt, sin)
+    w["_blocks"] = [block(w, f"layers.{l}.") for l in range(c.layers)]
+    return w

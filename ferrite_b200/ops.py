@@ -112,13 +112,13 @@ def rope_kv_write(qkv, cos, sin, places, rows, cache, H, KV, hd, q_out=None, qk_
     [2*KV, cache_rows, hd] at rows."""
     T = qkv.shape[0]
     assert qkv.dtype == torch.bfloat16 and qkv.shape[1] == (H + 2 * KV) * hd and qkv.stride(1) == 1
-    assert cache.dtype == torch.bfloat16 and cache.shape[0] == 2 * KV and cache.shape[2] == hd and cache.is_contiguous()
+    assert cache.dtype == torch.bfloat16 and cache.shape[0] == 2 * KV and cache.shape[2] == hd and cache.stride(2) == 1 and cache.stride(1) == hd
     assert places.dtype == torch.int32 and rows.dtype == torch.int32 and places.numel() == T and rows.numel() == T
     assert cos.shape == sin.shape and cos.is_contiguous() and sin.is_contiguous() and cos.dtype == torch.bfloat16
     if q_out is None:
         q_out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=qkv.device)
     check(lib().fb_rope_kv_write(qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1], places.data_ptr(),
-                                 rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0), cache.data_ptr(), cache.shape[1], _stream()))
+                                 rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0), cache.data_ptr(), cache.shape[1], cache.stride(0), _stream()))
     return q_out
 
 
@@ -128,7 +128,7 @@ _ATT_WS = {}
 def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=None):
     """One token per sequence: token t attends cache rows base[t] .. base[t] + place[t] of its kv head."""
     T = q.shape[0]
-    assert q.dtype == torch.bfloat16 and q.shape[1] == H * hd and q.stride(1) == 1 and cache.is_contiguous()
+    assert q.dtype == torch.bfloat16 and q.shape[1] == H * hd and q.stride(1) == 1 and cache.stride(2) == 1 and cache.stride(1) == hd
     assert base.dtype == torch.int32 and place.dtype == torch.int32 and base.numel() == T and place.numel() == T
     if out is None:
         out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=q.device)
@@ -136,7 +136,7 @@ def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=N
     ws = _ATT_WS.get(q.device)
     if need and (ws is None or ws.numel() < need):
         ws = _ATT_WS[q.device] = torch.empty(need, dtype=torch.uint8, device=q.device)
-    check(lib().fb_decode_attention(q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data_ptr(), cache.shape[1], base.data_ptr(), place.data_ptr(),
+    check(lib().fb_decode_attention(q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data_ptr(), cache.shape[1], cache.stride(0), base.data_ptr(), place.data_ptr(),
                                     max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None, ws.numel() if need else 0, _stream()))
     return out
 
@@ -155,3 +155,13 @@ def argmax(logits, out=None):
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     check(lib().fb_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), out.data_ptr(), _stream()))
     return out
+
+
+def attention_workspace(device, nbytes):
+    """The device's scratch for the attention kernels' key splits (grown when a call needs more)."""
+    if not nbytes:
+        return None
+    ws = _ATT_WS.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = _ATT_WS[device] = torch.empty(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
+    return ws

@@ -107,16 +107,23 @@ int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const v
 int fb_gather_rows(const void* table, int64_t table_rows, int64_t row_bytes, const int32_t* ids, int64_t n, void* out,
                    void* stream);
 
+/* dst[b, ids[i], :] = src[b, i, :] for every matrix b: Tensor.put, gather's inverse (ferrite/tensor.py:128-140,
+ * ferrite/compiler.py:1638-1650); of rows put at the same place the later one stays.  Strides in elements. */
+int fb_put_rows(void* dst, int64_t ds0, int64_t ds1, int64_t ds2, const void* src, int64_t ss0, int64_t ss1, int64_t ss2,
+                const int32_t* ids, int64_t batch, int64_t n, int64_t cols, int64_t dst_rows, int elem_bytes, void* stream);
+
 /* After the fused qkv matmul (models/llama.py:111-128): per head optional RMSNorm of q and k heads by
  * qk_norm[(H+KV)*hd] (Qwen3, llama.py:121-123), RoPE in Hugging Face's half-rotation form with bf16 tables
  * (llama.py:92-93, 351-368), then q heads -> q_out[T, H*hd] and the k and v heads into the cache rows
  * (Tensor.put, ferrite/tensor.py:128-140; ferrite/compiler.py:1638-1650): cache[(k heads, v heads)][rows[t]][:],
  * cache laid out [2*KV, cache_rows, hd] as models/llama.py:506-514.  cos / sin: [places, table_cols] with
  * table_cols = hd (one head's table) or (H + 2*KV)*hd (ferrite's, v's columns 1 and 0).  places[t] picks the
- * table row, rows[t] the cache row (place + the sequence's first row, llama.py:443-445). */
+ * table row, rows[t] the cache row (place + the sequence's first row, llama.py:443-445).  cache_head_stride: elements
+ * from one head's rows to the next's (cache_rows * hd, or more when the cache is one sequence's part of a larger one,
+ * models/llama.py:520-526). */
 int fb_rope_kv_write(const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos, const void* sin,
                      int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps,
-                     void* q_out, int64_t ld_q, void* cache, int64_t cache_rows, void* stream);
+                     void* q_out, int64_t ld_q, void* cache, int64_t cache_rows, int64_t cache_head_stride, void* stream);
 
 /* softmax(q k^T / sqrt(hd) + mask) v over the bf16 KV cache for one token per sequence: Tensor.attend
  * (ferrite/tensor.py:487-516, ferrite/compiler.py:1147-1170) as models/llama.py:129-146 uses it.  Token t reads
@@ -126,8 +133,19 @@ int fb_rope_kv_write(const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, 
  * workspace: fb_decode_attention_workspace_bytes(...) bytes (partial sums of the key splits). */
 size_t fb_decode_attention_workspace_bytes(int64_t T, int H, int KV, int hd, int64_t max_keys);
 int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
-                        const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
+                        int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same kernel in ferrite's general form, Tensor.attend (ferrite/tensor.py:487-516): `entries` batch entries of
+ * `rows` query rows [rows, hd] (strides in elements), every kv_rep consecutive entries reading one key and one value
+ * matrix [keys, hd] (a repeat_interleave read in place, ferrite/tensor.py:210-217), and an int32 place per row
+ * (place_row_stride 0: one place for all rows of an entry; place_entry_stride 0: one column of places for all
+ * entries): a row sees keys 0..place (the last `window` of them).  Scores are scaled by `scale`.  out: [entries, rows, hd]. */
+size_t fb_attend_workspace_bytes(int64_t entries, int64_t rows, int hd, int64_t max_keys);
+int fb_attend(const void* q, int64_t entries, int64_t rows, int hd, int64_t q_entry_stride, int64_t q_row_stride, const void* k,
+              const void* v, int64_t kv_entry_stride, int64_t kv_rep, int64_t keys, const int32_t* places,
+              int64_t place_entry_stride, int64_t place_row_stride, int window, float scale, void* out, void* workspace,
+              size_t workspace_bytes, void* stream);
 
 /* x * rsqrt(mean(x^2) + eps) * w, row by row (models/llama.py:82-85), bf16 in and out */
 int fb_rmsnorm(const void* x, int64_t rows, int64_t cols, int64_t ldx, const void* w, float eps, void* out, int64_t ldo,
@@ -135,6 +153,42 @@ int fb_rmsnorm(const void* x, int64_t rows, int64_t cols, int64_t ldx, const voi
 
 /* greedy pick: each row's first largest fp32 logit (what models/llama.py:787-795 does on the host with argmax) */
 int fb_argmax(const void* logits_f32, int64_t rows, int64_t cols, int64_t ld, int32_t* out, void* stream);
+
+/* ---- the mixture-of-experts router (models/llama.py:277-292) ------------------------------------------- */
+
+/* Tensor.topk (ferrite/tensor.py:373-388, ferrite/compiler.py:1716-1731): each row's k <= 64 largest, largest first,
+ * the lower column first among equals, -0 equal to 0, compared exactly as stored (dtype FB_BF16 or FB_FP32): the
+ * order of numpy's stable argsort (models/llama.py:27).  values (x's dtype) and ids: [rows, k] with row stride ldo;
+ * labels (optional, shaped like x): what to report instead of a pick's column.  softmax_weights_bf16 (optional,
+ * [rows, k]): the softmax of each row's picked values, the experts' weights (llama.py:287-288). */
+int fb_topk(int dtype, const void* x, int64_t rows, int64_t cols, int64_t ldx, int k, const int32_t* labels, void* values,
+            int32_t* ids, void* softmax_weights_bf16, int64_t ldo, void* stream);
+
+/* Tensor.touched (ferrite/tensor.py:403-416, ferrite/compiler.py:1898-1905): from ids and bf16 weights [rows, k]
+ * (experts below n), experts[min(rows*k, n)]: those some row picks by a weight that is not 0, ascending, then n
+ * ("none"); out_bf16[entry, row]: the row's weight for that entry's expert, 0 where it did not pick it. */
+int fb_touched(const int32_t* ids, const void* weights_bf16, int64_t rows, int k, int n, int32_t* experts, void* out_bf16, void* stream);
+
+/* ---- the general operator surface (ferrite/tensor.py:292-372, 443-485), for expressions that are not one of the
+ * fused kernels above.  Strides are in elements for (batch, row, col); a stride of 0 broadcasts.  *_host arguments
+ * are host arrays read during the call. */
+
+/* One fused elementwise expression (ferrite fuses a tree into one kernel, ferrite/compiler.py:699-738).  The
+ * expression is a postfix program of n_ops (op, arg) pairs: op 0 pushes input `arg`, op 1 pushes consts_host[position];
+ * 10.. are binary (add sub mul max cmplt cmpne keep drop div min), 30.. unary (exp log sin cos sqrt recip relu exp2
+ * log2 round-to-bf16 trunc neg).  Computed in fp32, rounded once at the store. */
+int fb_elementwise(int n_ops, const int32_t* program_host, const float* consts_host, int n_inputs, const void* const* inputs_host,
+                   const int64_t* strides_host, const int32_t* dtypes_host, void* out, const int64_t* out_strides_host,
+                   int out_dtype, int64_t batch, int64_t rows, int64_t cols, void* stream);
+
+/* sum or max along one axis, kept as 1 (Tensor.sum / Tensor.max, ferrite/tensor.py:359-368) */
+int fb_reduce(int is_max, const void* in, const int64_t* in_strides_host, int in_dtype, int64_t batch, int64_t rows, int64_t cols,
+              int axis, void* out, const int64_t* out_strides_host, int out_dtype, void* stream);
+
+/* C[b] = A[b] @ B[b] for bf16 / fp32 operands by strides (a transposed B is a stride swap, a batch stride of 0
+ * repeats a matrix): Tensor.matmul without a block-float B (ferrite/tensor.py:443-485); fp32 accumulation. */
+int fb_matmul(const void* a, const int64_t* a_strides_host, int a_dtype, const void* b, const int64_t* b_strides_host, int b_dtype,
+              void* c, const int64_t* c_strides_host, int c_dtype, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
 
 #ifdef __cplusplus
 }

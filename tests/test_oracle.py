@@ -109,3 +109,14 @@ def test_batched_decode_matches_reference_vectors(name):
     for i in range(4):
         got = llama.forward(g[f"{name}.step{i}.ids"].tolist(), g[f"{name}.step{i}.places"].tolist(), w, c, kv, slots)
         assert np.allclose(got, g[f"{name}.steps"][i], rtol=1e-9, atol=1e-9), (name, i)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_c_restatement_equals_the_numpy_one(fmt):
+    from oracle import build
+    g = golden("bfp.npz")
+    for name in ("spread", "edge", "wide", "weights"):
+        x = bfp.bf16_floats(g[f"{name}.bits"])
+        assert np.array_equal(build.bfp_values(x, fmt).astype(np.float64), g[f"{name}.{fmt}"]), name
+    big = np.random.default_rng(1).normal(0, 0.02, (512, 1024)).astype(np.float32)
+    assert np.array_equal(build.bfp_values(big, fmt), bfp.bfp(big, fmt).astype(np.float32))

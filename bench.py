@@ -1,0 +1,330 @@
+"""Decode throughput of the block-float hot path on B200s, one JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama8b|smollm] [--layers L] [--impl reference]
+
+The default workload is the Llama-3.1-8B-shape batched decode (32 sequences, 2048 tokens of context each, bfp8 weights,
+bf16 KV cache), tensor-parallel over N GPUs with an NCCL all-reduce after o_proj and down_proj.  A step is one decode
+step of all the sequences: embedding gather, 32 blocks (fused RMSNorm + qkv matmul, RoPE + KV write, split-KV attention,
+o_proj + residual, RMSNorm + gate_up + SwiGLU, down_proj + residual), final norm, output layer, greedy pick.
+
+    value      tokens/s with the step's inputs resident on the device (the pick of one step feeds the next on the device)
+    e2e        the same through the public call with host buffers: ids and places copied in from pinned memory and the
+               picked tokens read back, every step
+    roofline   the block-float matmul kernel (the dominant kernel): its algorithmic bytes over its measured duration
+    cpu_baseline / --impl reference: the numpy restatement of the reference's CPU path on this box's host cores, on a
+               bounded sample (one block and the output layer, scaled to the model)
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE.json configs[2]: Llama-3.1-8B shape
+    "llama8b": dict(model=dict(dim=4096, heads=32, kv=8, layers=32, vocab=128256, ffn=14336, theta=500000.0, eps=1e-5), mode="bfp8",
+                    sequences=32, context=2048, name="llama-3.1-8b-shape bfp8, 32 sequences x 2048 context, bf16 KV"),
+    # BASELINE.json configs[0]: SmolLM-135M shape, batch 1 (the reference's own CPU-runnable case)
+    "smollm": dict(model=dict(dim=576, heads=9, kv=3, layers=30, vocab=49152, ffn=1536, theta=10000.0, eps=1e-5, tied=True), mode="bfp8",
+                   sequences=1, context=32, name="smollm-135m-shape bfp8, batch 1, 32-token prompt, bf16 KV"),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=0, help="fewer blocks than the model has (a smoke run; the JSON line says so)")
+    ap.add_argument("--impl", default="ferrite_b200", choices=["ferrite_b200", "reference"])
+    return ap.parse_args()
+
+
+def measured_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class Clocks(threading.Thread):
+    """SM clock and throttle reasons sampled through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        import pynvml
+        self.nv, self.samples, self.reasons, self.stop = pynvml, [], set(), False
+        pynvml.nvmlInit()
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+
+    def run(self):
+        nv = self.nv
+        names = {nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown", nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap"}
+        while not self.stop:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.reasons |= {n for bit, n in names.items() if mask & bit}
+            except Exception:  # a sample that cannot be read is left out
+                pass
+            time.sleep(0.05)
+
+    def summary(self):
+        self.stop = True
+        nv = self.nv
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)), "reasons": sorted(self.reasons)}
+
+
+def linear_bytes(c, sequences, fmt_bytes=1.0625):
+    """Algorithmic bytes of one step's block-float matmuls: packed weights once, activations in and out (bf16)."""
+    hd = c.head_dim or c.dim // c.heads
+    shapes = [(c.dim, (c.heads + 2 * c.kv) * hd, (c.heads + 2 * c.kv) * hd), (c.heads * hd, c.dim, c.dim), (c.dim, 2 * c.ffn, c.ffn), (c.ffn, c.dim, c.dim)]
+    per_layer = sum(k * n * fmt_bytes + 2 * sequences * k + 2 * sequences * out for k, n, out in shapes)
+    head = c.dim * c.vocab_shard * fmt_bytes + 2 * sequences * c.dim + 4 * sequences * c.vocab_shard
+    return c.layers * per_layer + head, 4 * c.layers + 1
+
+
+def step_bytes(c, sequences, context):
+    """Algorithmic bytes a decode step reads per GPU: weights once, the KV rows each token sees, its embedding row."""
+    hd = c.head_dim or c.dim // c.heads
+    weights, _ = linear_bytes(c, 0)
+    kv = sequences * context * c.layers * 2 * c.kv * hd * 2
+    return weights + kv + sequences * c.dim * 2
+
+
+def run_ferrite(args):
+    import torch
+    import torch.distributed as dist
+    from ferrite_b200 import llama, ops
+    from ferrite_b200.tensor import Runtime, Tensor, jit
+
+    world, rank, local = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run --nproc-per-node {args.gpus}"
+    rt = Runtime(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=rt.device)
+    wl = WORKLOADS[args.workload]
+    full = llama.model(**wl["model"], places=wl["context"] + args.steps + args.warmup + 64)
+    if args.layers:
+        full.layers = args.layers
+    c = llama.tensor_parallel(full, rank, world, dist.group.WORLD) if world > 1 else full
+    if world == 1:
+        c.vocab_shard = full.vocab
+    prec = llama.precision(full, wl["mode"])
+    w = llama.random_weights(rt, c, prec, seed=0, full=full)
+    S, ctx = wl["sequences"], wl["context"]
+    part = ctx + args.steps + args.warmup + 64
+    part += -part % 64
+    hd = llama.head(full)
+    caches = []
+    gen = torch.Generator(device=rt.device).manual_seed(1 + rank)
+    for _ in range(full.layers):  # the prompts' keys and values: N(0, 1), as a prefill would have left them
+        t = Tensor(rt, S * part, hd, batch=2 * c.kv)
+        t.buf.normal_(0, 1, generator=gen)
+        caches.append(t)
+    slots = S if S > 1 else None
+
+    def step_fn(ids, places):
+        return llama.next_tokens(llama.forward(ids, places, w, c, caches, slots), c)
+
+    step = jit(step_fn)
+    on = lambda row: Tensor.of(rt, [row], "int32")
+    rng = np.random.default_rng(0)
+    ids0 = [int(v) for v in rng.integers(0, full.vocab, S)]
+    place = ctx
+    # the first two calls plan and record; they are part of the warm-up
+    before = ops.KERNELS[0]
+    picks = step(on(ids0), on([place] * S))
+    place += 1
+    per_step = None
+    for i in range(max(args.warmup, 3) - 1):
+        k0 = ops.KERNELS[0]
+        picks = step(on(picks.numpy().reshape(-1).tolist()), on([place] * S))
+        if i == 0:
+            per_step = ops.KERNELS[0] - k0  # kernels the recorded step holds (counted while it was recorded)
+        place += 1
+    rt.wait()
+
+    # ---- device-resident loop: the pick feeds the next step on the device, places advance on the device
+    ids_t, places_t = on(picks.numpy().reshape(-1).tolist()), on([place] * S)
+    one = Tensor.of(rt, [[1] * S], "int32")
+    bump = jit(lambda p: p + one)  # (records on its second call)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        places_t = bump(places_t)
+    clocks = Clocks(local)
+    clocks.start()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step(ids_t, places_t)
+        ids_t.buf.copy_(out.buf, non_blocking=True)
+        places_t = bump(places_t)
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1)
+    place += args.steps + 3
+
+    # ---- end to end: host ids and places in (pinned), picked tokens out, every step
+    h_ids = torch.tensor([ids0], dtype=torch.int32).pin_memory()
+    h_places = torch.tensor([[place] * S], dtype=torch.int32).pin_memory()
+    h_out = torch.empty(1, 1, S, dtype=torch.int32).pin_memory()
+    d_ids, d_places = on(ids0), on([place] * S)
+    e2e_steps = max(8, args.steps // 2)
+    sync_all()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(e2e_steps):
+        d_ids.buf.copy_(h_ids.view(1, 1, S), non_blocking=True)
+        d_places.buf.copy_(h_places.view(1, 1, S), non_blocking=True)
+        out = step(d_ids, d_places)
+        h_out.copy_(out.buf, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        h_ids.copy_(h_out.view(1, S))  # the next step's input is this step's pick, from the host
+        h_places += 1
+    e3.record()
+    sync_all()
+    ms_e2e = e2.elapsed_time(e3)
+    clk = clocks.summary()
+
+    # ---- the dominant kernel alone: the step's block-float matmuls, back to back, every weight of the model once
+    x32 = Tensor.of(rt, rng.normal(0, 1, (S, full.dim)).astype(np.float32).tolist())
+    f32 = Tensor.of(rt, rng.normal(0, 1, (S, c.ffn)).astype(np.float32).tolist()) if c.ffn else None
+    a32 = Tensor.of(rt, rng.normal(0, 1, (S, c.heads * hd)).astype(np.float32).tolist())
+
+    def matmuls():
+        last = None
+        for p in w["_blocks"]:
+            last = x32.matmul(p["qkv_proj"]).realize()
+            last = a32.matmul(p["o_proj"]).realize()
+            last = x32.matmul(p["gate_up_proj"]).realize()
+            last = f32.matmul(p["down_proj"]).realize()
+        return x32.matmul(w["embed.T"], dtype="fp32").realize()
+
+    mm = jit(lambda: matmuls())
+    for _ in range(3):
+        mm()
+    torch.cuda.synchronize()
+    e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e4.record()
+    for _ in range(reps):
+        mm()
+    e5.record()
+    torch.cuda.synchronize()
+    lin_bytes, lin_launches = linear_bytes(c, S)
+    lin_ms = e4.elapsed_time(e5) / reps
+
+    # max over ranks
+    times = torch.tensor([ms, ms_e2e, lin_ms], device=rt.device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e, lin_ms = times.tolist()
+    peaks, peak_kind = measured_peaks()
+    achieved = lin_bytes / (lin_ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode tokens/s", "value": S * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}", "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
+                   "weights": "random N(0, 0.02) quantised on the device", "kv": "N(0, 1) bf16 standing in for the prompts' prefill"},
+        "e2e": {"value": S * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S, "d2h_bytes_per_step": 4 * S, "steps": e2e_steps},
+        "gpu_launches": int(per_step or 0) * args.steps,
+        "clocks": clk,
+        "roofline": {"bound": "hbm", "kernel": "linear_tcgen05_kernel (block-float dequant GEMM, %d tokens)" % S, "achieved": achieved,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_kind,
+                     "traffic": None, "launches": lin_launches, "us_per_launch": lin_ms * 1e3 / lin_launches, "bytes_per_launch": lin_bytes / lin_launches},
+        "step_roofline": {"algorithmic_bytes_per_gpu": step_bytes(c, S, ctx + args.warmup + args.steps // 2),
+                          "frac_of_hbm": step_bytes(c, S, ctx + args.warmup + args.steps // 2) / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+    }
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(args, sample_seconds=20)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_sample(args, seconds):
+    """One decode step of ONE block plus the output layer of the workload, by the numpy restatement of the reference's
+    CPU path (oracle/), timed; scaled to the model's block count.  Weights are quantised by the C restatement."""
+    from oracle import build as obuild
+    from oracle import llama as ollama
+    wl = WORKLOADS[args.workload]
+    c = ollama.model(**{k: v for k, v in wl["model"].items() if k != "tied"}, places=wl["context"] + 64)
+    layers = args.layers or c.layers
+    c.layers = 1
+    S, ctx = wl["sequences"], wl["context"]
+    rng = np.random.default_rng(0)
+    hd, nh = ollama.head(c), c.heads + 2 * c.kv
+    q = lambda *shape: obuild.bfp_values(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02), wl["mode"])
+    w = {"layers.0.input_layernorm": np.ones((1, c.dim), np.float32), "layers.0.post_attention_layernorm": np.ones((1, c.dim), np.float32),
+         "layers.0.qkv_proj": q(c.dim, nh * hd), "layers.0.o_proj": q(c.heads * hd, c.dim), "layers.0.gate_up_proj": q(c.dim, 2 * c.ffn),
+         "layers.0.down_proj": q(c.ffn, c.dim), "norm": np.ones((1, c.dim), np.float32)}
+    w["embed"] = (rng.standard_normal((c.vocab, c.dim), dtype=np.float32) * np.float32(0.02))
+    w["embed.T"] = obuild.bfp_values(np.ascontiguousarray(w["embed"].T), wl["mode"])
+    w["cos"], w["sin"] = ollama.rotary(c, c.places)
+    part = ctx + 64
+    caches = ollama.kv_cache(c, S * part)  # np.zeros: float64, as the reference's
+    caches[0][:, :, :] = rng.standard_normal(caches[0].shape)
+    ids = [int(v) for v in rng.integers(0, c.vocab, S)]
+    slots = S if S > 1 else None
+    times, place = [], ctx
+    start = time.perf_counter()
+    while not times or (time.perf_counter() - start < seconds and len(times) < 16):
+        t0 = time.perf_counter()
+        x = w["embed"][ids]
+        rows, cos, sin, mask, live = ollama.around(w, c, [place] * S if slots else [place], S * part if slots else part, slots)
+        t_in = time.perf_counter()
+        x = ollama.layer(x, ollama.block(w, "layers.0."), c, cos, sin, mask, caches[0], rows, live, slots)
+        t_layer = time.perf_counter()
+        logits = ollama.rms(x, w["norm"], c.eps) @ w["embed.T"]
+        picks = logits.argmax(-1)
+        t_head = time.perf_counter()
+        times.append(((t_in - t0) + (t_head - t_layer), t_layer - t_in))
+        place += 1
+    rest, layer = np.median([t[0] for t in times]), np.median([t[1] for t in times])
+    step_seconds = rest + layers * layer
+    return {"value": S / step_seconds, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{len(times)} decode steps of 1 of {layers} blocks plus embedding and output layer in numpy (float32 weights, float64 KV cache as the "
+                      f"reference keeps it); block time x {layers} + the rest", "seconds_per_step_scaled": step_seconds}
+
+
+def cpu_baseline(args, sample_seconds):
+    return cpu_sample(args, sample_seconds)
+
+
+def run_reference(args):
+    """The reference arm: the reference's CPU path (its numpy branch, restated under oracle/) on this box's host cores."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    base = cpu_sample(args, seconds=min(120, 4 * max(args.steps, 1)))
+    S = wl["sequences"]
+    line = {"impl": "reference", "metric": "decode tokens/s", "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * S / base["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl["name"], "layers": args.layers or wl["model"]["layers"], "parallelism": "host cores"},
+            "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse()
+    run_reference(a) if a.impl == "reference" else run_ferrite(a)

@@ -88,7 +88,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
 }
 
 // Greedy pick: the column of each row's largest logit, the lowest column among equals (numpy's argmax).
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t ld, int64_t cols, int32_t* __restrict__ out) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t ld, int64_t cols, int32_t* __restrict__ out,
+                                                      float* __restrict__ out_value) {
   const int64_t t = blockIdx.x;
   float best = -INFINITY;
   int64_t at = cols;
@@ -113,7 +114,10 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
       const int64_t oi = __shfl_xor_sync(0xffffffffu, at, o);
       if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
     }
-    if (threadIdx.x == 0) out[t] = (int32_t)(at < cols ? at : 0);
+    if (threadIdx.x == 0) {
+      out[t] = (int32_t)(at < cols ? at : 0);
+      if (out_value) out_value[t] = best;
+    }
   }
 }
 
@@ -170,8 +174,8 @@ extern "C" int fb_rmsnorm(const void* x, int64_t rows, int64_t cols, int64_t ldx
   return fb::launch_status("fb_rmsnorm");
 }
 
-extern "C" int fb_argmax(const void* logits_f32, int64_t rows, int64_t cols, int64_t ld, int32_t* out, void* stream) {
+extern "C" int fb_argmax(const void* logits_f32, int64_t rows, int64_t cols, int64_t ld, int32_t* out, float* out_value, void* stream) {
   FB_REQUIRE(logits_f32 && out && rows >= 1 && cols >= 1 && ld >= cols, "fb_argmax: bad arguments");
-  fb::argmax_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits_f32, ld, cols, out);
+  fb::argmax_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits_f32, ld, cols, out, out_value);
   return fb::launch_status("fb_argmax");
 }

@@ -18,7 +18,7 @@ from .tensor import BFP, Tensor, jit  # noqa: F401  (jit re-exported: `from ferr
 
 # a config's fields past a plain Llama's, as a plain Llama has them (models/llama.py:541-543)
 DEFAULTS = dict(head_dim=None, rope=None, sliding=None, k=0, experts=0, moe=0, norm_topk=True, tied=False, precision=None, places=4096,
-                ffn=None, vocab=None, qk_norm=False)
+                ffn=None, vocab=None, qk_norm=False, tp=None)
 
 
 def model(**c):
@@ -116,10 +116,52 @@ def experts(h, p, ids, w):
 
 def layer(x, p, c, rotary, seen, cache, rows, live=None, slots=None):
     """One block: attention then a SwiGLU MLP (or a mixture of experts), each after an RMSNorm and added back
-    (models/llama.py:95-109)."""
-    x = x + attention(rms(x, p["input_layernorm"], c), p, c, rotary, seen, cache, rows, slots)
+    (models/llama.py:95-109).  Tensor-parallel (c.tp): every rank holds its heads' and its MLP columns' share of the
+    weights, so o_proj and down_proj give partial sums: an all-reduce over NVLink after each, the residual added once."""
+    x = added(x, attention(rms(x, p["input_layernorm"], c), p, c, rotary, seen, cache, rows, slots), c)
     h = rms(x, p["post_attention_layernorm"], c)
-    return x + (moe(h, p, c, live) if "router" in p else mlp(h, p))
+    return added(x, moe(h, p, c, live) if "router" in p else mlp(h, p), c)
+
+
+def added(x, y, c):
+    """x + y; with tensor parallelism y is this rank's partial sum: rank 0 adds x, then the ranks' results are summed."""
+    tp = getattr(c, "tp", None)
+    if not tp:
+        return x + y
+    import torch.distributed as dist
+    out = (x + y if tp.rank == 0 else y).realize()
+    if not out.buf.is_contiguous() or out.owner is not None:
+        out = (out + 0).realize()
+    dist.all_reduce(out.buf, group=tp.group)
+    return out
+
+
+def tensor_parallel(c, rank, world, group=None):
+    """c as rank `rank` of `world` holds it: its share of the query and key heads, of the MLP's columns and of the
+    vocabulary (models too large or too slow for one GPU; the reference has no counterpart: one chip, ferrite/runtime.py:304-311)."""
+    assert c.heads % world == 0 and c.kv % world == 0 and (c.ffn or 0) % world == 0 and c.vocab % (16 * world) == 0, "shards of whole heads and runs"
+    local = SimpleNamespace(**vars(c))
+    local.head_dim, local.heads, local.kv, local.dim = head(c), c.heads // world, c.kv // world, c.dim
+    local.ffn, local.vocab_shard = (c.ffn or 0) // world, c.vocab // world
+    local.tp = SimpleNamespace(rank=rank, world=world, group=group)
+    return local
+
+
+def next_tokens(out, c):
+    """The greedy pick of each row of logits, int32 [1, 1, rows], on the device.  Tensor-parallel: `out` is this rank's
+    shard of the vocabulary; each rank picks its best and the ranks' bests are compared (8 bytes a token a rank)."""
+    tp = getattr(c, "tp", None)
+    if not tp:
+        return out.greedy()
+    import torch.distributed as dist
+    rt, n = out.rt, out.rows
+    best = Tensor(rt, 1, n, dtype="fp32")
+    ids = (out.greedy(best) + tp.rank * c.vocab_shard).realize()
+    all_best, all_ids = Tensor(rt, tp.world, n, dtype="fp32"), Tensor(rt, tp.world, n, dtype="int32")
+    dist.all_gather_into_tensor(all_best.buf, best.buf, group=tp.group)
+    dist.all_gather_into_tensor(all_ids.buf, ids.buf, group=tp.group)
+    _, pick = (all_best.T + 0).realize().topk(1, labels=(all_ids.T + 0).realize())  # the lowest rank (lowest column) among equals
+    return pick.reshape(1, 1, n)
 
 
 def firsts(rt, n, slots, part, cache={}):
@@ -214,42 +256,56 @@ def rotary(c, n, wide=False):
     return (np.concatenate([cos] * (c.heads + c.kv) + [still(1)] * c.kv, 1), np.concatenate([sin] * (c.heads + c.kv) + [still(0)] * c.kv, 1))
 
 
-def random_weights(rt, c, prec=None, seed=0, scale=0.02):
+def random_weights(rt, c, prec=None, seed=0, scale=0.02, full=None):
     """Random weights in c's shapes made on the device (for models too large to draw on the host): linear weights
-    N(0, scale) rounded to bf16 then cast to their formats, norm weights 1, RoPE tables for c.places places."""
+    N(0, scale) rounded to bf16 then cast to their formats, norm weights 1, RoPE tables for c.places places.
+    c from tensor_parallel (full: the whole model's config): every rank draws the whole matrices from the same seed and
+    keeps its columns or rows, so the ranks together hold exactly the one-GPU model."""
     gen = torch.Generator(device=rt.device).manual_seed(seed)
-    hd, d, nh = head(c), c.dim, c.heads + 2 * c.kv
+    full = full or c
+    tp = getattr(c, "tp", None)
+    r, n = (tp.rank, tp.world) if tp else (0, 1)
+    hd, d = head(full), full.dim
+    H, KV = full.heads, full.kv
 
-    def draw(name, *shape, sigma=scale):
-        x = torch.empty(*shape, dtype=torch.float32, device=rt.device).normal_(0, sigma, generator=gen).bfloat16()
-        shape3 = (1,) * (3 - len(shape)) + tuple(shape)
+    def keep(name, x, pick=None):
+        if pick is not None:
+            x = pick(x).contiguous()
+        shape3 = (1,) * (3 - x.dim()) + tuple(x.shape)
         t = Tensor(rt, shape3[1], shape3[2], batch=shape3[0], buf=x.view(shape3))
         f = weight_format(name, prec)
         return t.cast(f).realize() if f != "bf16" else t
 
-    ones = lambda n: Tensor.of(rt, np.ones((1, n), np.float32))
+    def draw(*shape):
+        return torch.empty(*shape, dtype=torch.float32, device=rt.device).normal_(0, scale, generator=gen).bfloat16()
+
+    part = lambda x, axis, parts=1: torch.cat([x.narrow(axis, p * (x.shape[axis] // parts) + r * (x.shape[axis] // parts // n), x.shape[axis] // parts // n)
+                                              for p in range(parts)], axis)
+    def qkv_cols(x):  # this rank's query heads, key heads and value heads
+        q, k, v = x[:, :H * hd], x[:, H * hd:(H + KV) * hd], x[:, (H + KV) * hd:]
+        return torch.cat([part(q, 1), part(k, 1), part(v, 1)], 1)
+
+    ones = lambda m: Tensor.of(rt, np.ones((1, m), np.float32))
     w = {}
-    for l in range(c.layers):
+    for l in range(full.layers):
         pre = f"layers.{l}."
         w[pre + "input_layernorm"], w[pre + "post_attention_layernorm"] = ones(d), ones(d)
-        w[pre + "qkv_proj"] = draw(pre + "qkv_proj", d, nh * hd)
-        w[pre + "o_proj"] = draw(pre + "o_proj", c.heads * hd, d)
-        if c.qk_norm:
+        w[pre + "qkv_proj"] = keep(pre + "qkv_proj", draw(d, (H + 2 * KV) * hd), qkv_cols if tp else None)
+        w[pre + "o_proj"] = keep(pre + "o_proj", draw(H * hd, d), (lambda x: part(x, 0)) if tp else None)
+        if full.qk_norm:
             w[pre + "qk_norm"] = Tensor.of(rt, np.ones((c.heads + c.kv, 1, hd), np.float32))
-        if c.experts:
-            w[pre + "router"] = draw(pre + "router", d, c.experts)
-            w[pre + "experts.gate_up"] = draw(pre + "experts.gate_up", c.experts, d, 2 * c.moe)
-            w[pre + "experts.down"] = draw(pre + "experts.down", c.experts, c.moe, d)
+        if full.experts:
+            w[pre + "router"] = keep(pre + "router", draw(d, full.experts))
+            w[pre + "experts.gate_up"] = keep(pre + "experts.gate_up", draw(full.experts, d, 2 * full.moe))
+            w[pre + "experts.down"] = keep(pre + "experts.down", draw(full.experts, full.moe, d))
         else:
-            w[pre + "gate_up_proj"] = draw(pre + "gate_up_proj", d, 2 * c.ffn)
-            w[pre + "down_proj"] = draw(pre + "down_proj", c.ffn, d)
+            w[pre + "gate_up_proj"] = keep(pre + "gate_up_proj", draw(d, 2 * full.ffn), (lambda x: part(x, 1, 2)) if tp else None)
+            w[pre + "down_proj"] = keep(pre + "down_proj", draw(full.ffn, d), (lambda x: part(x, 0)) if tp else None)
     w["norm"] = ones(d)
-    embed = torch.empty(c.vocab, d, dtype=torch.float32, device=rt.device).normal_(0, scale, generator=gen).bfloat16()
-    w["embed"] = Tensor(rt, c.vocab, d, buf=embed.view(1, c.vocab, d))
-    et = Tensor(rt, d, c.vocab, buf=embed.t().contiguous().view(1, d, c.vocab))
-    f = weight_format("embed.T", prec)
-    w["embed.T"] = et.cast(f).realize() if f != "bf16" else et
-    cos, sin = rotary(c, c.places)
+    embed = draw(full.vocab, d)
+    w["embed"] = Tensor(rt, full.vocab, d, buf=embed.view(1, full.vocab, d))
+    w["embed.T"] = keep("embed.T", embed.t(), (lambda x: part(x, 1)) if tp else (lambda x: x))
+    cos, sin = rotary(full, full.places)
     w["cos"], w["sin"] = Tensor.of(rt, cos), Tensor.of(rt, sin)
-    w["_blocks"] = [block(w, f"layers.{l}.") for l in range(c.layers)]
+    w["_blocks"] = [block(w, f"layers.{l}.") for l in range(full.layers)]
     return w

@@ -7,6 +7,12 @@ from ._lib import BF16, BFP4, BFP8, FP32, check, lib
 
 _TORCH = {"bf16": torch.bfloat16, "fp32": torch.float32, "int32": torch.int32}
 
+KERNELS = [0]  # kernels of this library launched so far by this process (every wrapper below counts its own)
+
+
+def count(n=1):
+    KERNELS[0] += n
+
 
 def _stream():
     return torch.cuda.current_stream().cuda_stream
@@ -44,6 +50,7 @@ def quantize(x, fmt):
     assert n, f"{tuple(x.shape)} to {fmt}: columns in runs of 16"
     data = torch.empty(batch * n, dtype=torch.uint8, device=x.device)
     check(lib().fb_quantize(_lib.DTYPES[fmt], x.data_ptr(), batch, K, N, data.data_ptr(), _stream()))
+    count()
     return Packed(fmt, batch, K, N, data)
 
 
@@ -94,6 +101,7 @@ def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="no
     check(lib().fb_linear(w.code, x.data_ptr(), M, K, x.stride(0), w.data.data_ptr(), w.N, out.data_ptr(), _lib.DTYPES[out_dtype],
                           out.stride(0), _ptr(norm_w), eps, epi, _ptr(residual), residual.stride(0) if residual is not None else 0,
                           _ptr(workspace), workspace.numel() if workspace is not None else 0, _stream()))
+    count(-(-M // 4) if M <= 4 else -(-M // 128) * (2 if norm_w is not None else 1))  # GEMV passes, or GEMM passes (+ the norm's)
     return out
 
 
@@ -104,6 +112,7 @@ def gather_rows(table, ids, out=None):
         out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
     check(lib().fb_gather_rows(table.data_ptr(), table.shape[0], table.shape[1] * table.element_size(), ids.data_ptr(), ids.numel(),
                                out.data_ptr(), _stream()))
+    count()
     return out
 
 
@@ -119,6 +128,7 @@ def rope_kv_write(qkv, cos, sin, places, rows, cache, H, KV, hd, q_out=None, qk_
         q_out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=qkv.device)
     check(lib().fb_rope_kv_write(qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1], places.data_ptr(),
                                  rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0), cache.data_ptr(), cache.shape[1], cache.stride(0), _stream()))
+    count()
     return q_out
 
 
@@ -138,6 +148,7 @@ def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=N
         ws = _ATT_WS[q.device] = torch.empty(need, dtype=torch.uint8, device=q.device)
     check(lib().fb_decode_attention(q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data_ptr(), cache.shape[1], cache.stride(0), base.data_ptr(), place.data_ptr(),
                                     max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None, ws.numel() if need else 0, _stream()))
+    count(2 if need else 1)  # the attention kernel, and the merge of its key splits
     return out
 
 
@@ -146,14 +157,17 @@ def rmsnorm(x, w, eps=1e-5, out=None):
     if out is None:
         out = torch.empty_like(x)
     check(lib().fb_rmsnorm(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), w.data_ptr(), eps, out.data_ptr(), out.stride(0), _stream()))
+    count()
     return out
 
 
-def argmax(logits, out=None):
+def argmax(logits, out=None, values=None):
+    """Each row's first largest fp32 logit's column (int32); values: an fp32 vector that receives the maxima."""
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
     if out is None:
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-    check(lib().fb_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), out.data_ptr(), _stream()))
+    check(lib().fb_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), out.data_ptr(), _ptr(values), _stream()))
+    count()
     return out
 
 

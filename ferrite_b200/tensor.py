@@ -48,7 +48,9 @@ class Runtime:
         lib()
         self.numbers, self.launches, self.names = {}, 0, []
 
-    def launched(self, name):
+    def launched(self, name, kernels=0):
+        """One op queued; kernels: how many kernels it launched that no ops.* wrapper has counted already."""
+        ops.count(kernels)
         self.launches += 1
         if len(self.names) < 4096:
             self.names.append(name)
@@ -379,7 +381,7 @@ class Tensor:
         t, x, ids = self.realize(), x.realize(), ids.realize()
         check(lib().fb_put_rows(t.buf.data_ptr(), *_strides3(t.buf), x.buf.data_ptr(), *_strides3(x.buf), ids.buf.data_ptr(), t.batch, x.rows, t.cols,
                                 t.rows, t.buf.element_size(), ops._stream()))
-        self.rt.launched("put")
+        self.rt.launched("put", 1)
         return self
 
     # ---------------------------------------------------------------- matmul, attention, the router
@@ -426,7 +428,7 @@ class Tensor:
                               kb.stride(0), rep, k.rows, places.buf.data_ptr(), places.buf.stride(0) if places.batch > 1 else 0,
                               places.buf.stride(1), window or 0, 1.0, out.buf.data_ptr(), ops._ptr(ws), ws.numel() if ws is not None else 0,
                               ops._stream()))
-        self.rt.launched("attention")
+        self.rt.launched("attention", 2 if need else 1)
         return out
 
     def topk(self, k, parts=1, labels=None):
@@ -453,7 +455,7 @@ class Tensor:
         if parts > 1:
             offs = Tensor.of(self.rt, [[p * cols for p in range(parts) for _ in range(k)]], "int32")
             ids = (ids + offs).realize()
-        self.rt.launched("topk")
+        self.rt.launched("topk", parts)
         return values, ids
 
     def touched(self, n, weights):
@@ -466,7 +468,7 @@ class Tensor:
         slots = min(self.rows * self.cols, n)
         experts, out = Tensor(self.rt, slots, 1, dtype="int32"), Tensor(self.rt, self.rows, 1, batch=slots)
         check(lib().fb_touched(x.buf.data_ptr(), w.buf.data_ptr(), self.rows, self.cols, n, experts.buf.data_ptr(), out.buf.data_ptr(), ops._stream()))
-        self.rt.launched("touched")
+        self.rt.launched("touched", 1)
         return experts, out
 
     # ---------------------------------------------------------------- a decode step's two fused kernels
@@ -505,6 +507,16 @@ class Tensor:
         ops.decode_attention(q.buf[0], cache.buf, base.buf.reshape(-1), last.buf.reshape(-1), heads, kv, hd, max_keys=min(length or cache.rows, cache.rows),
                              window=window or 0, out=out.buf[0])
         self.rt.launched("attention")
+        return out
+
+    def greedy(self, values=None):
+        """Each row's first largest logit's column, int32 [1, 1, rows], picked on the device (the reference reads the
+        logits back and takes numpy's argmax, models/llama.py:787-795): fp32 logits of one matrix."""
+        x = self.realize()
+        assert x.dtype == "fp32" and x.batch == 1 and x.buf.stride(2) == 1, "a matrix of fp32 logits"
+        out = Tensor(self.rt, 1, x.rows, dtype="int32")
+        ops.argmax(x.buf[0], out.buf.reshape(-1), None if values is None else values.buf.reshape(-1))
+        self.rt.launched("argmax")
         return out
 
     # ---------------------------------------------------------------- computing the tree
@@ -549,7 +561,7 @@ def _realize(t, into=None):
         i64 = lambda v: (ctypes_i64 * 3)(*v)
         check(lib().fb_reduce(int(op == "reduce_max"), src.buf.data_ptr(), i64(_strides3(src.buf)), _lib.DTYPES[src.dtype], *src.shape, axis,
                               out.buf.data_ptr(), i64(_strides3(out.buf)), _lib.DTYPES[out.dtype], ops._stream()))
-        t.rt.launched(f"{op}{axis}")
+        t.rt.launched(f"{op}{axis}", 1)
         _done(t, buf=out.buf)
     elif op == "matmul":
         _run_matmul(t, into)
@@ -683,7 +695,7 @@ def _run_matmul(t, into):
     i64 = lambda buf, batch: (ctypes_i64 * 3)(*([0] + _strides3(buf)[1:] if batch == 1 and t.batch > 1 else _strides3(buf)))
     check(lib().fb_matmul(a.buf.data_ptr(), i64(a.buf, a.batch), _lib.DTYPES[a.dtype], b.buf.data_ptr(), i64(b.buf, b.batch), _lib.DTYPES[b.dtype],
                           out.buf.data_ptr(), i64(out.buf, t.batch), _lib.DTYPES[out.dtype], t.batch, t.rows, t.cols, a.cols, ops._stream()))
-    t.rt.launched("matmul")
+    t.rt.launched("matmul", 1)
     _done(t, buf=out.buf)
 
 
@@ -732,7 +744,7 @@ def _run_elementwise(t, into=None):
     dtypes = (ctypes.c_int32 * max(n, 1))(*[_lib.DTYPES[u.dtype] for u in inputs])
     check(lib().fb_elementwise(len(code), prog, cst, n, ptrs, strides, dtypes, out.buf.data_ptr(), (ctypes_i64 * 3)(*_strides3(out.buf)),
                                _lib.DTYPES[out.dtype], *t.shape, ops._stream()))
-    t.rt.launched("elementwise")
+    t.rt.launched("elementwise", 1)
     _done(t, buf=out.buf)
 
 

@@ -151,8 +151,9 @@ int fb_attend(const void* q, int64_t entries, int64_t rows, int hd, int64_t q_en
 int fb_rmsnorm(const void* x, int64_t rows, int64_t cols, int64_t ldx, const void* w, float eps, void* out, int64_t ldo,
                void* stream);
 
-/* greedy pick: each row's first largest fp32 logit (what models/llama.py:787-795 does on the host with argmax) */
-int fb_argmax(const void* logits_f32, int64_t rows, int64_t cols, int64_t ld, int32_t* out, void* stream);
+/* greedy pick: each row's first largest fp32 logit (what models/llama.py:787-795 does on the host with argmax);
+ * out_value (optional): the maxima, for picking across vocabulary shards */
+int fb_argmax(const void* logits_f32, int64_t rows, int64_t cols, int64_t ld, int32_t* out, float* out_value, void* stream);
 
 /* ---- the mixture-of-experts router (models/llama.py:277-292) ------------------------------------------- */
 

@@ -31,6 +31,8 @@ SIGNATURES = {
     "fb_rope_kv_write": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _p, _i64, _p, _p, _p, _f, _p, _i64, _p, _i64, _i64, _p]),
     "fb_decode_attention_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i64]),
     "fb_decode_attention": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _i64, _i64, _p, _p, _i64, _i, _p, _i64, _p, _sz, _p]),
+    "fb_decode_attention_static_max_bytes": (_sz, []),
+    "fb_decode_attention_static": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _i64, _i64, _p, _p, _i64, _i, _p, _i64, _p]),
     "fb_attend_workspace_bytes": (_sz, [_i64, _i64, _i, _i64]),
     "fb_attend": (_i, [_p, _i64, _i64, _i, _i64, _i64, _p, _p, _i64, _i64, _i64, _p, _i64, _i64, _i, _f, _p, _p, _sz, _p]),
     "fb_topk": (_i, [_i, _p, _i64, _i64, _i64, _i, _p, _p, _p, _p, _i64, _p]),

@@ -342,3 +342,38 @@ extern "C" int fb_attend(const void* q, int64_t entries, int64_t rows, int hd, i
   a.out = (uint16_t*)out, a.o_s0 = rows * hd * kv_rep, a.o_s1 = rows * hd, a.o_sr = hd;
   return fb::launch_attention(a, entries, hd, keys, workspace, workspace_bytes, (cudaStream_t)stream);
 }
+
+// ---- fb_decode_attention with its scratch built into the library -------------------------------------------------
+// Some hosts cannot give this library a workspace: a serving process that has handed all of the device's memory to
+// its own pool at start-up (weights, KV cache) and forbids any later cudaMalloc, or a binding that has no way to own
+// and pass a scratch buffer.  For them the partial sums of the key splits live in this array, which every GPU that
+// loads the library holds from load to exit.  All calls on a device share it and it keeps whatever the last call
+// left: nothing in it has to start at zero (every split writes all of its rows before the merge reads them), but
+// two calls that overlap on the GPU (two streams) would overwrite each other's partial sums.
+namespace fb {
+constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;
+static __device__ __align__(256) unsigned char g_attention_scratch[STATIC_SCRATCH_BYTES];
+static void* g_scratch_ptr[64] = {};  // the array's device address, per device, looked up once
+}  // namespace fb
+
+extern "C" size_t fb_decode_attention_static_max_bytes(void) { return fb::STATIC_SCRATCH_BYTES; }
+
+extern "C" int fb_decode_attention_static(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
+                                          int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window,
+                                          void* out, int64_t ld_o, void* stream) {
+  FB_REQUIRE(KV >= 1 && H >= 1 && H % KV == 0, "fb_decode_attention_static: whole groups of query heads per key head");
+  const size_t need = fb_decode_attention_workspace_bytes(T, H, KV, hd, max_keys);
+  FB_REQUIRE(need <= fb::STATIC_SCRATCH_BYTES,
+             "fb_decode_attention_static: this call needs %zu bytes of scratch, the built-in array holds %zu: fewer tokens per call, or "
+             "fb_decode_attention with a workspace of the caller's",
+             need, fb::STATIC_SCRATCH_BYTES);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fb::launch_status("fb_decode_attention_static (cudaGetDevice)");
+  if (!fb::g_scratch_ptr[dev]) {  // set-up, on the first call on this device: in host code the array's name is not its device address
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, fb::g_attention_scratch) != cudaSuccess || !p) return fb::launch_status("fb_decode_attention_static (cudaGetSymbolAddress)");
+    fb::g_scratch_ptr[dev] = p;
+  }
+  return fb_decode_attention(q, T, ld_q, H, KV, hd, cache, cache_rows, cache_head_stride, base, place, max_keys, window, out, ld_o,
+                             fb::g_scratch_ptr[dev], fb::STATIC_SCRATCH_BYTES, stream);
+}

@@ -136,6 +136,19 @@ int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, i
                         int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* fb_decode_attention for callers that cannot provide a workspace and must not have one allocated for them (a
+ * process whose own pool owns all device memory, a binding with no way to hold a scratch buffer).  It has no
+ * counterpart in the reference.  The partial sums of the key splits go into an array built into the library
+ * (fb_decode_attention_static_max_bytes() bytes of every GPU that loads it, from load to exit); a call that would
+ * need more is refused with FB_ERR_ARG and a message.  No memory is allocated or freed by this call, ever.
+ * The first call on a device looks up the array's device address: make that call outside any stream capture.
+ * All calls on a device share the array and it keeps the last call's contents; nothing in it needs clearing, but
+ * calls that overlap on the GPU (different streams) race on it: keep them on one stream. */
+size_t fb_decode_attention_static_max_bytes(void);
+int fb_decode_attention_static(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
+                               int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window,
+                               void* out, int64_t ld_o, void* stream);
+
 /* The same kernel in ferrite's general form, Tensor.attend (ferrite/tensor.py:487-516): `entries` batch entries of
  * `rows` query rows [rows, hd] (strides in elements), every kv_rep consecutive entries reading one key and one value
  * matrix [keys, hd] (a repeat_interleave read in place, ferrite/tensor.py:210-217), and an int32 place per row

@@ -45,6 +45,15 @@ struct GemmParams {
   int splits, steps_per_split, steps_total;  // K in steps of 128 rows
   int x_slots, a_slots;
   const float* rstd;  // [M] row scales of the RMSNorm prologue, or null
+  // a mixture of experts' matmul (Tensor.matmul(index=), ferrite/tensor.py:450-460): W is a batch of n_experts packed
+  // matrices expert_bytes apart and index[slot] picks one per slot (n_experts or more: none, zeros).
+  //   mode 1: one result per slot (grid z): out + slot * out_slot_stride, x rows from slot * x_slot_rows on
+  //   mode 2: the slots' matmuls summed: K runs through slot 0's rows, then slot 1's, ... (x columns slot * K + k)
+  int mode;
+  const int32_t* index;
+  int n_experts, n_slots, steps_per_slot;
+  int64_t expert_bytes, x_slot_rows, out_slot_stride;
+  const uint16_t* row_scale;  // mode 1: bf16 [slot * M + t] multiplying the epilogue's result, or null
 };
 
 enum WaitCode { WAIT_X_EMPTY = 103, WAIT_X_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_ACC };
@@ -89,6 +98,25 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   const uint32_t abort_flag = smem_u32(tmem_slot + 1);
 
+  // an indexed matmul's slot that picks no expert is zeros, with nothing read (ferrite/tensor.py:458-460)
+  const int zslot = p.mode == 1 ? (int)blockIdx.z : 0;
+  int expert = 0;
+  if (p.mode == 1) {
+    expert = p.index[zslot];
+    if (expert < 0 || expert >= p.n_experts) {
+      if (split == 0) {
+        const int64_t cols = swiglu ? 64 : TILE_N, n0 = cols * tile, n_end = swiglu ? a.N / 2 : a.N;
+        for (int64_t i = tid; i < a.M * cols; i += THREADS) {
+          const int64_t t = i / cols, n = n0 + i % cols;
+          if (n >= n_end) continue;
+          const int64_t at = zslot * p.out_slot_stride + t * a.ldo + n;
+          if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = 0.f;
+          else static_cast<uint16_t*>(a.out)[at] = 0;
+        }
+      }
+      return;  // (every CTA of a cluster shares the slot: they all leave here, before any cluster barrier)
+    }
+  }
   if (tid == 0) {
     for (int s = 0; s < SX; ++s) mbar_init(smem_u32(x_full + s), 1), mbar_init(smem_u32(x_empty + s), 1);
     for (int s = 0; s < SA; ++s) mbar_init(smem_u32(a_full + s), WORKERS / 32), mbar_init(smem_u32(a_empty + s), 1);
@@ -114,15 +142,21 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   const int64_t g0 = swiglu ? tile : 2 * (int64_t)tile, g1 = swiglu ? tile + G / 2 : 2 * (int64_t)tile + 1;
   const bool has_g1 = g1 < G;
 
+  // steps are numbered through the slots in mode 2: step gs is rows (gs % S) * 128.. of slot gs / S
+  const int S = p.mode == 2 ? p.steps_per_slot : p.steps_total;
   if (warp == WARP_X && lane == 0) {
     Ring rx;
+    int ks = s0 % S, slot = s0 / S;
+    const int y = p.mode == 1 ? (int)(zslot * p.x_slot_rows) : 0;
     for (int i = 0; i < n_steps; ++i, rx.next(SX)) {
       const int s = rx.slot;
       mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
       mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
+      const int x0 = (p.mode == 2 ? slot * (int)K : 0) + ks * STEP_ROWS;
 #pragma unroll
-      for (int u = 0; u < STEP_UNITS; ++u)  // rows of K past the end read as zeros
-        tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, ((s0 + i) * STEP_UNITS + u) * KSTEP, 0, smem_u32(x_full + s));
+      for (int u = 0; u < STEP_UNITS; ++u)  // rows of K past the end read as zeros (or meet zeros in A)
+        tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, x0 + u * KSTEP, y, smem_u32(x_full + s));
+      if (++ks == S) ks = 0, ++slot;
     }
   } else if (warp == WARP_MMA && lane == 0) {
     const uint32_t idesc = umma_idesc_bf16(nt, true, false);
@@ -147,8 +181,8 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   } else if (warp < WORKERS / 32) {
     // this thread's two (run, row) places in every 128-row step: where their bytes lie in the step's units of the
     // packed matrix, and where their 16 columns go in the A slot
-    const uint8_t* W = static_cast<const uint8_t*>(a.W);
-    const uint8_t* src[2];
+    const uint8_t* W = static_cast<const uint8_t*>(a.W) + (p.mode == 1 ? expert * p.expert_bytes : 0);
+    int64_t src[2];
     uint32_t exp_rel[2], a_off[2][2];
     bool col_ok[2];
     int unit_of[2];
@@ -158,7 +192,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       const int unit = k >> 6, ku = k & 63;
       unit_of[j] = unit;
       col_ok[j] = grp == 0 || has_g1;
-      src[j] = W + ((grp ? g1 : g0) * KS + (int64_t)s0 * STEP_UNITS + unit) * UNIT + (run * KSTEP + ku) * RUN;
+      src[j] = ((grp ? g1 : g0) * KS + unit) * UNIT + (run * KSTEP + ku) * RUN;
       exp_rel[j] = UNIT_MANT + run * KSTEP + ku - (run * KSTEP + ku) * RUN;
       const int slot = swiglu ? (run << 1 | grp) : run8;  // gate and up runs alternate: rows r and r + 16 pair up
       const uint32_t row = ((k >> 3) * 2 + (slot >> 2)) * 1024 + (k & 7) * 128;
@@ -169,12 +203,20 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     using RawT = typename std::conditional<FMT == FB_BFP8, uint4, uint2>::type;
     RawT q[AHEAD][2];
     uint32_t top[AHEAD][2];
-    const int units_here = units_total - s0 * STEP_UNITS;  // units of K from this CTA's first step to the end of K
+    // the loads' own walk through the steps (they run AHEAD of the unpacking): rows f_ks * 128.. of slot f_slot
+    int f_ks = s0 % S, f_slot = s0 / S;
+    const uint8_t* f_w = W;  // the slot's expert's matrix, null if it picks none
+    auto pick = [&]() {
+      if (p.mode != 2) return;
+      const int e = f_slot < p.n_slots ? p.index[f_slot] : -1;
+      f_w = e >= 0 && e < p.n_experts ? static_cast<const uint8_t*>(a.W) + e * p.expert_bytes : nullptr;
+    };
+    pick();
     auto fetch = [&](int step, int buf) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const bool ok = col_ok[j] && step < n_steps && step * STEP_UNITS + unit_of[j] < units_here;
-        const uint8_t* at = src[j] + (int64_t)step * (STEP_UNITS * UNIT);
+        const bool ok = col_ok[j] && step < n_steps && f_w != nullptr && f_ks * STEP_UNITS + unit_of[j] < units_total;
+        const uint8_t* at = f_w + src[j] + (int64_t)f_ks * (STEP_UNITS * UNIT);
         if (ok) {
           q[buf][j] = __ldg(reinterpret_cast<const RawT*>(at));
           top[buf][j] = __ldg(at + exp_rel[j]);
@@ -184,6 +226,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
           top[buf][j] = 0;
         }
       }
+      if (++f_ks == S) f_ks = 0, ++f_slot, pick();
     };
 #pragma unroll
     for (int d = 0; d < AHEAD; ++d) fetch(d, d);
@@ -235,7 +278,8 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   }
   if (splits > 1) cluster_sync();  // every CTA of the cluster is past its MMAs: the A slots are free to receive
   else __syncthreads();
-  const int col_groups = nt >= 32 ? 4 : nt / 8;  // worker warps sharing one quarter of the TMEM lanes split the token columns
+  // worker warps sharing one quarter of the TMEM lanes split the token columns, in runs of whole 8-column loads
+  const int col_groups = nt % 32 == 0 ? 4 : nt % 16 == 0 ? 2 : 1;
   if (worker && (warp >> 2) < col_groups) {
     const int q = warp & 3, ncol = nt / col_groups, col0 = (warp >> 2) * ncol, row = 32 * q + lane;
     const uint32_t owner = row / rows_per;
@@ -285,19 +329,21 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
           if (swiglu) up += src[lr + 16];
         }
         if (p.rstd) val *= p.rstd[t], up *= p.rstd[t];
+        const float scale = p.row_scale ? bf16_bits_to_float(p.row_scale[(int64_t)zslot * M + t]) : 1.f;
         const int tr = split * rows_per + lr;  // row inside the tile
         int64_t n;
         if (swiglu) {
-          val = val / (1.f + __expf(-val)) * up;
+          val = val / (1.f + __expf(-val)) * up * scale;
           n = 64 * (int64_t)tile + (tr / 32) * 16 + tr % 16;
           if (n >= a.N / 2) continue;
         } else {
           n = TILE_N * (int64_t)tile + tr;
           if (n >= a.N) continue;
-          val += res[e];
+          val = val * scale + res[e];
         }
-        if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[t * a.ldo + n] = val;
-        else static_cast<uint16_t*>(a.out)[t * a.ldo + n] = (uint16_t)float_to_bf16_bits(val);
+        const int64_t at = zslot * p.out_slot_stride + t * a.ldo + n;
+        if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = val;
+        else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(val);
       }
     }
   }
@@ -350,12 +396,14 @@ struct Plan {
   size_t smem;
 };
 
-Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue) {
+// slots, mode: an indexed matmul's (mode 1: so many results, more CTAs; mode 2: so many times the steps of K)
+Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots = 1, int mode = 0) {
   Plan pl;
   pl.nt = (int)((M + 15) / 16 * 16);
   pl.tmem_cols = pl.nt <= 32 ? 32 : pl.nt <= 64 ? 64 : 128;
   pl.tiles = (int)(epilogue == FB_EPI_SWIGLU ? groups_of(N) / 2 : (groups_of(N) + 1) / 2);
-  pl.steps = (int)ceil_div(K, STEP_ROWS);
+  pl.steps = (int)ceil_div(K, STEP_ROWS) * (mode == 2 ? slots : 1);
+  const int64_t ctas_per_split = (int64_t)pl.tiles * (mode == 1 ? slots : 1);
   // K splits (a cluster of up to 8 CTAs per tile): the count with the least modelled time, waves x (a CTA's fixed
   // cost + its steps); SwiGLU's gate/up row pairs must stay inside one CTA's slice of rows
   int best = 1;
@@ -365,7 +413,7 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue) {
     if (epilogue == FB_EPI_SWIGLU && s != 1 && s != 2 && s != 4) continue;
     const int per = (int)ceil_div(pl.steps, s);
     if ((int)ceil_div(pl.steps, per) != s) continue;  // every split gets work
-    const double cost = (double)ceil_div((int64_t)pl.tiles * s, 148) * (5.0 + (s > 1 ? 1.0 : 0.0) + 0.6 * per);
+    const double cost = (double)ceil_div(ctas_per_split * s, 148) * (5.0 + (s > 1 ? 1.0 : 0.0) + 0.6 * per);
     if (cost < best_cost) best_cost = cost, best = s;
   }
   pl.splits = best;
@@ -389,10 +437,16 @@ size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N) {
   return WS_RSTD + (size_t)(M < 128 ? M : 128) * K * 2;
 }
 
-static int run_pass(const LinearArgs& a, cudaStream_t s) {
-  Plan pl = make_plan(a.fmt, a.M, a.K, a.N, a.epilogue);
+static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) {
+  const int mode = ix ? ix->mode : 0, slots = ix ? ix->n_slots : 1;
+  Plan pl = make_plan(a.fmt, a.M, a.K, a.N, a.epilogue, slots, mode);
   GemmParams p{};
   p.a = a;
+  if (ix) {
+    p.mode = mode, p.index = ix->index, p.n_experts = ix->n_experts, p.n_slots = slots, p.steps_per_slot = (int)ceil_div(a.K, STEP_ROWS);
+    p.expert_bytes = packed_bytes(a.fmt, a.K, a.N), p.x_slot_rows = ix->x_slot_rows, p.out_slot_stride = ix->out_slot_stride;
+    p.row_scale = static_cast<const uint16_t*>(ix->row_scale);
+  }
   p.nt = pl.nt, p.tmem_cols = pl.tmem_cols, p.splits = pl.splits, p.steps_per_split = pl.sps, p.steps_total = pl.steps;
   p.x_slots = pl.x_slots, p.a_slots = pl.a_slots;
   const void* x = a.x;
@@ -410,7 +464,8 @@ static int run_pass(const LinearArgs& a, cudaStream_t s) {
     p.rstd = rstd, x = xn, ldx = a.K;
   }
   CUtensorMap tmap;
-  const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
+  // the activations as TMA sees them: [rows, K]; an indexed matmul's slots add rows (mode 1) or columns (mode 2)
+  const cuuint64_t dims[2] = {(cuuint64_t)a.K * (mode == 2 ? slots : 1), (cuuint64_t)(mode == 1 && ix->x_slot_rows ? ix->x_slot_rows * (slots - 1) + a.M : a.M)};
   const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
   const cuuint32_t box[2] = {KSTEP, (cuuint32_t)pl.nt}, estr[2] = {1, 1};  // 64 bf16 = one 128-byte swizzled row per token
   CUresult rc = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
@@ -427,7 +482,7 @@ static int run_pass(const LinearArgs& a, cudaStream_t s) {
     attr_set[a.fmt == FB_BFP8] = true;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(pl.tiles, pl.splits), cfg.blockDim = dim3(THREADS), cfg.dynamicSmemBytes = pl.smem, cfg.stream = s;
+  cfg.gridDim = dim3(pl.tiles, pl.splits, mode == 1 ? slots : 1), cfg.blockDim = dim3(THREADS), cfg.dynamicSmemBytes = pl.smem, cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = pl.splits, attr[0].val.clusterDim.z = 1;
@@ -444,10 +499,12 @@ int linear_tcgen05(const LinearArgs& args, cudaStream_t s) {
     a.x = static_cast<const uint16_t*>(args.x) + m0 * args.ldx;
     a.out = static_cast<char*>(args.out) + m0 * args.ldo * esz;
     if (args.residual) a.residual = static_cast<const uint16_t*>(args.residual) + m0 * args.ldr;
-    if (int rc = run_pass(a, s)) return rc;
+    if (int rc = run_pass(a, nullptr, s)) return rc;
   }
   return FB_OK;
 }
+
+int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStream_t s) { return run_pass(a, &ix, s); }
 
 }  // namespace fb
 

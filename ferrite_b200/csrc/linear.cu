@@ -24,3 +24,20 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
   if (M > 4 && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);
   return fb::linear_gemv(a, s);
 }
+
+extern "C" int fb_linear_indexed(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, int64_t x_slot_rows, const void* W, int64_t N,
+                                 int n_experts, const int32_t* index, int n_slots, int sum_slots, void* out, int out_dtype, int64_t ldo,
+                                 int64_t out_slot_stride, const void* norm_w, float eps, int epilogue, const void* residual, int64_t ldr,
+                                 const void* row_scale_bf16, void* workspace, size_t workspace_bytes, void* stream) {
+  FB_REQUIRE(fmt == FB_BFP8 || fmt == FB_BFP4, "fb_linear_indexed: W is bfp8 or bfp4 (dtype %d given)", fmt);
+  FB_REQUIRE(x && W && out && index && n_experts >= 1 && n_slots >= 1, "fb_linear_indexed: null pointer or no experts");
+  FB_REQUIRE(M >= 1 && M <= 128 && K >= 8 && K % 8 == 0 && N >= 16 && N % 16 == 0, "fb_linear_indexed: up to 128 rows, K a multiple of 8, N of 16");
+  FB_REQUIRE(out_dtype == FB_BF16 || out_dtype == FB_FP32, "fb_linear_indexed: out is bf16 or fp32");
+  FB_REQUIRE(epilogue >= FB_EPI_NONE && epilogue <= FB_EPI_RESIDUAL && (epilogue != FB_EPI_SWIGLU || N % 128 == 0), "fb_linear_indexed: epilogue %d (SwiGLU: N a multiple of 128)", epilogue);
+  FB_REQUIRE(!sum_slots || (epilogue != FB_EPI_SWIGLU && !row_scale_bf16 && K % 64 == 0), "fb_linear_indexed: summed slots take whole 64-row units of K, no SwiGLU, no row scale");
+  FB_REQUIRE(epilogue != FB_EPI_RESIDUAL || residual, "fb_linear_indexed: the residual epilogue needs a residual");
+  FB_REQUIRE(ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0, "fb_linear_indexed: misaligned x or W");
+  fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, norm_w, eps, epilogue, residual, ldr, workspace, workspace_bytes};
+  fb::IndexedArgs ix{sum_slots ? 2 : 1, index, n_experts, n_slots, x_slot_rows, out_slot_stride, row_scale_bf16};
+  return fb::linear_tcgen05_indexed(a, ix, (cudaStream_t)stream);
+}

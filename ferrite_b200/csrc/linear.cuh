@@ -22,8 +22,19 @@ struct LinearArgs {
   size_t workspace_bytes;
 };
 
+// Tensor.matmul(index=) (ferrite/tensor.py:450-460): W a batch of packed matrices, index[slot] picks one per slot
+struct IndexedArgs {
+  int mode;  // 1: one result per slot; 2: the slots' matmuls summed (K runs through the slots)
+  const int32_t* index;
+  int n_experts, n_slots;
+  int64_t x_slot_rows;      // mode 1: rows of x from one slot's to the next's (0: every slot multiplies the same x)
+  int64_t out_slot_stride;  // mode 1: elements of out from one slot's result to the next's
+  const void* row_scale;    // mode 1: bf16 [slot * M + t] multiplying the epilogue's result, or null
+};
+
 int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: M <= 4 per pass, CUDA cores
 int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores
+int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStream_t s);
 bool linear_tcgen05_supports(const LinearArgs& a);
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N);
 

@@ -96,7 +96,7 @@ def moe(h, p, c, live=None):
     """A mixture of experts in the MLP's place (models/llama.py:277-292): router logits, the k best experts and the
     softmax of their logits on the device, then every touched expert's SwiGLU for the step's tokens, weighted and summed
     (the reference's decode form, chip_experts, models/llama.py:302-329)."""
-    logits = h.matmul(p["router"])
+    logits = h.matmul(p["router"], dtype="fp32")  # (fp32: the picks are compared exactly as stored, tensor.py topk)
     if c.norm_topk:
         values, ids = logits.topk(c.k)
         w = values.softmax()

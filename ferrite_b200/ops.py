@@ -179,3 +179,20 @@ def attention_workspace(device, nbytes):
     if ws is None or ws.numel() < nbytes:
         ws = _ATT_WS[device] = torch.empty(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
     return ws
+
+
+def linear_indexed(x, w, index, out, sum_slots=False, x_slot_rows=0, out_slot_stride=0, M=None, out_dtype="bf16", norm_w=None, eps=1e-5,
+                   epilogue="none", residual=None, row_scale=None):
+    """A mixture of experts' matmul: x [M, K] (or n_slots of them, or [M, n_slots * K] with sum_slots) by the matrices
+    of the batch w (Packed) that index (int32 [n_slots], on the device) picks; see fb_linear_indexed."""
+    M = x.shape[0] if M is None else M
+    n_slots = index.numel()
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and index.dtype == torch.int32 and index.is_contiguous()
+    epi = {"none": _lib.EPI_NONE, "swiglu": _lib.EPI_SWIGLU, "residual": _lib.EPI_RESIDUAL}[epilogue]
+    ws = linear_workspace(x.device, lib().fb_linear_workspace_bytes(max(M, 5), w.K, w.N)) if norm_w is not None else None
+    check(lib().fb_linear_indexed(w.code, x.data_ptr(), M, w.K, x.stride(0), x_slot_rows, w.data.data_ptr(), w.N, w.batch, index.data_ptr(), n_slots,
+                                  int(sum_slots), out.data_ptr(), _lib.DTYPES[out_dtype], out.stride(-2), out_slot_stride, _ptr(norm_w), eps, epi,
+                                  _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(row_scale), _ptr(ws),
+                                  ws.numel() if ws is not None else 0, _stream()))
+    count(2 if norm_w is not None else 1)
+    return out

@@ -555,6 +555,8 @@ def _realize(t, into=None):
         if _fused_linear(t, into):
             return
         _run_elementwise(t, into)
+    elif op == "reduce_sum" and t.args["axis"] == 0 and _match_experts(t.srcs[0]):
+        _run_experts(t, _match_experts(t.srcs[0]), None, into)
     elif op in ("reduce_sum", "reduce_max"):
         src, axis = t.srcs[0].realize(), t.args["axis"]
         out = into or Tensor(t.rt, t.rows, t.cols, batch=t.batch, dtype=t.dtype)
@@ -656,6 +658,13 @@ def _fused_linear(t, into):
                     and 2 * gate.cols == mm.cols and mm.cols % 32 == 0:
                 _linear(t, mm, "swiglu", None, into)
                 return True
+    if t.op == "add" and t.dtype == "bf16":  # x + the experts' sum
+        for x, y in (t.srcs, t.srcs[::-1]):
+            if isinstance(x, Tensor) and isinstance(y, Tensor) and y.op == "reduce_sum" and y.args["axis"] == 0 and x.shape == t.shape:
+                found = _match_experts(y.srcs[0])
+                if found:
+                    _run_experts(t, found, x, into)
+                    return True
     if t.op == "add" and t.dtype == "bf16":  # x + mm
         for x, mm in (t.srcs, t.srcs[::-1]):
             if isinstance(x, Tensor) and _packed_matmul(mm) and x.shape == mm.shape == t.shape and x.dtype == "bf16" and mm.dtype == "bf16":
@@ -696,6 +705,84 @@ def _run_matmul(t, into):
     check(lib().fb_matmul(a.buf.data_ptr(), i64(a.buf, a.batch), _lib.DTYPES[a.dtype], b.buf.data_ptr(), i64(b.buf, b.batch), _lib.DTYPES[b.dtype],
                           out.buf.data_ptr(), i64(out.buf, t.batch), _lib.DTYPES[out.dtype], t.batch, t.rows, t.cols, a.cols, ops._stream()))
     t.rt.launched("matmul", 1)
+    _done(t, buf=out.buf)
+
+
+def _indexed_packed(t):
+    """(a, w, index) if t is a matmul, not yet computed, picking block-float matrices by an index, else None."""
+    if isinstance(t, Tensor) and t.op == "matmul" and len(t.srcs) == 3 and t.srcs[1].dtype in BFP and t.srcs[0].dtype == "bf16":
+        return t.srcs
+    return None
+
+
+def _match_experts(t):
+    """A mixture's touched experts as models/llama.py:317-324 writes them for a decode step:
+    (glu(x[:, :, :m], x[:, :, m:]) * weights).matmul(down, index=picks) with x = h.matmul(gate_up, index=picks).
+    Returns (h, gate_up, down, picks, weights or None), else None."""
+    found = _indexed_packed(t)
+    if not found:
+        return None
+    a, down, picks = found
+    weights = None
+    if isinstance(a, Tensor) and a.op == "mul":
+        for g, w in (a.srcs, a.srcs[::-1]):
+            if isinstance(w, Tensor) and w.op is None and w.shape == (t.batch, t.rows, 1) and w.dtype == "bf16" and isinstance(g, Tensor) and g.op == "mul":
+                a, weights = g, w
+                break
+    if not (isinstance(a, Tensor) and a.op == "mul"):
+        return None
+    for g, u in (a.srcs, a.srcs[::-1]):
+        gate = _match_silu_of(g)
+        if gate is None or not isinstance(u, Tensor) or gate.op != "cols" or u.op != "cols" or u.srcs[0] is not gate.srcs[0]:
+            continue
+        first = _indexed_packed(gate.srcs[0])
+        if first and first[2] is picks and first[0].batch == 1 and gate.args["start"] == 0 and u.args["start"] == gate.cols \
+                and 2 * gate.cols == first[1].cols and first[1].cols % 128 == 0 and gate.cols == down.rows and gate.cols % 64 == 0 and t.rows <= 128:
+            return first[0], first[1], down, picks, weights
+    return None
+
+
+def _run_experts(t, found, residual, into):
+    """Two kernels for a mixture's decode step: every touched expert's gate_up with SwiGLU and its tokens' weights into
+    act [tokens, entries * m]; then the experts' downs summed over the entries in the accumulators (+ the residual)."""
+    h, gate_up, down, picks, weights = found
+    rms = _match_rms(h)
+    x, norm_w, eps = rms if rms else (h, None, 0.0)
+    x, picks = x.realize(), picks.realize()
+    xb = x.buf[0] if x.buf.stride(2) == 1 and x.buf.stride(1) % 8 == 0 else (x + 0).realize().buf[0]
+    slots, m, rows = picks.rows * picks.cols, down.rows, x.rows
+    idx = picks.buf.reshape(-1) if picks.buf.is_contiguous() else (picks + 0).realize().buf.reshape(-1)
+    act = Tensor(t.rt, rows, slots * m)
+    scale = None
+    if weights is not None:
+        scale = weights.buf if weights.buf.is_contiguous() else (weights + 0).realize().buf
+    ops.linear_indexed(xb, gate_up.realize().packed, idx, act.buf[0], out_slot_stride=m, norm_w=None if norm_w is None else norm_w.buf, eps=eps,
+                       epilogue="swiglu", row_scale=scale)
+    res = None
+    if residual is not None:
+        residual = residual.realize()
+        res = residual.buf[0] if residual.buf.stride(2) == 1 else (residual + 0).realize().buf[0]
+    out = into if into is not None and into.buf.stride(2) == 1 else Tensor(t.rt, t.rows, t.cols, dtype=t.dtype)
+    ops.linear_indexed(act.buf[0], down.realize().packed, idx, out.buf[0], sum_slots=True, out_dtype=t.dtype,
+                       epilogue="residual" if res is not None else "none", residual=res)
+    t.rt.launched("experts " + gate_up.dtype)
+    _done(t, buf=out.buf)
+
+
+def _run_indexed_matmul(t, into):
+    """Tensor.matmul(index=) on its own: one result per entry (ferrite/tensor.py:450-460); block-float matrices."""
+    a, w, picks = t.srcs
+    assert w.dtype in BFP and t.rows <= 128, "picked matrices are block floats here, for up to 128 rows"
+    rms = _match_rms(a) if a.batch == 1 else None
+    x, norm_w, eps = rms if rms else (a, None, 0.0)
+    x, picks = x.realize(), picks.realize()
+    if not (x.buf.is_contiguous() and x.cols % 8 == 0):
+        x = (x + 0).realize()
+    idx = picks.buf.reshape(-1) if picks.buf.is_contiguous() else (picks + 0).realize().buf.reshape(-1)
+    out = into if into is not None and into.buf.is_contiguous() else Tensor(t.rt, t.rows, t.cols, batch=t.batch, dtype=t.dtype)
+    ops.linear_indexed(x.buf.reshape(-1, x.cols), w.realize().packed, idx, out.buf, M=t.rows, x_slot_rows=0 if x.batch == 1 else t.rows,
+                       out_slot_stride=t.rows * t.cols, out_dtype=t.dtype, norm_w=None if norm_w is None else norm_w.buf, eps=eps)
+    t.rt.launched("matmul index " + w.dtype)
     _done(t, buf=out.buf)
 
 

@@ -100,6 +100,21 @@ int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const v
               int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,
               int64_t ldr, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Tensor.matmul(index=) (ferrite/tensor.py:450-460; ferrite/compiler.py:704-706): a mixture of experts' matmul.  W is
+ * a batch of n_experts packed [K, N] matrices fb_packed_bytes(fmt, K, N) apart; index[slot] (int32, read on the
+ * device, so a replayed step follows its tokens' choices) picks one for each of n_slots slots, and a slot that picks
+ * none (index >= n_experts) gives zeros with nothing read.  x: [M <= 128, K] per slot, x_slot_rows rows apart (0: every
+ * slot multiplies the same x).  Prologue / epilogue as fb_linear; row_scale_bf16 (optional, [n_slots, M]) multiplies
+ * each result row after the epilogue: the experts' weights (models/llama.py:322-324).
+ *   sum_slots = 0: one result per slot, out + slot * out_slot_stride elements (what ferrite's batch of entries is);
+ *   sum_slots = 1: x is [M, n_slots * K] (slot s's activations in columns s*K..) and the slots' matmuls are summed
+ *                  into one [M, N] result in the accumulators: the experts' down projections and their sum over
+ *                  the entries (llama.py:324 `.sum(0)`) in one kernel. */
+int fb_linear_indexed(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, int64_t x_slot_rows, const void* W, int64_t N,
+                      int n_experts, const int32_t* index, int n_slots, int sum_slots, void* out, int out_dtype, int64_t ldo,
+                      int64_t out_slot_stride, const void* norm_w, float eps, int epilogue, const void* residual, int64_t ldr,
+                      const void* row_scale_bf16, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- the rest of a decode step ------------------------------------------------------------------------- */
 
 /* out[i, :] = table[ids[i], :]: Tensor.gather, the embedding lookup (ferrite/tensor.py:116-126,

@@ -257,8 +257,11 @@ def run_ferrite(args):
         line["cpu_baseline"] = cpu_baseline(args, sample_seconds=20)
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if world > 1:  # leave without tearing NCCL down: the recorded graphs still hold its kernels, and a teardown waits on them
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def cpu_sample(args, seconds):

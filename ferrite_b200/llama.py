@@ -147,6 +147,26 @@ def tensor_parallel(c, rank, world, group=None):
     return local
 
 
+def tp_keep(name, full, rank, world):
+    """What rank `rank` of `world` keeps of the weight called `name`: (axis, indices) into the whole matrix, or None for
+    a weight every rank holds whole.  qkv_proj: its heads' columns of q, of k and of v; gate_up_proj: its columns of the
+    gate half and of the up half; o_proj and down_proj: the matching rows; embed.T: its run of the vocabulary."""
+    hd, H, KV = head(full), full.heads, full.kv
+    run = lambda first, size: np.arange(first + rank * (size // world), first + (rank + 1) * (size // world))
+    op = name.split(".")[-1]
+    if op == "qkv_proj":
+        return 1, np.concatenate([run(0, H * hd), run(H * hd, KV * hd), run((H + KV) * hd, KV * hd)])
+    if op == "o_proj":
+        return 0, run(0, H * hd)
+    if op == "gate_up_proj":
+        return 1, np.concatenate([run(0, full.ffn), run(full.ffn, full.ffn)])
+    if op == "down_proj":
+        return 0, run(0, full.ffn)
+    if name == "embed.T":
+        return 1, run(0, full.vocab)
+    return None
+
+
 def next_tokens(out, c):
     """The greedy pick of each row of logits, int32 [1, 1, rows], on the device.  Tensor-parallel: `out` is this rank's
     shard of the vocabulary; each rank picks its best and the ranks' bests are compared (8 bytes a token a rank)."""
@@ -279,19 +299,21 @@ def random_weights(rt, c, prec=None, seed=0, scale=0.02, full=None):
     def draw(*shape):
         return torch.empty(*shape, dtype=torch.float32, device=rt.device).normal_(0, scale, generator=gen).bfloat16()
 
-    part = lambda x, axis, parts=1: torch.cat([x.narrow(axis, p * (x.shape[axis] // parts) + r * (x.shape[axis] // parts // n), x.shape[axis] // parts // n)
-                                              for p in range(parts)], axis)
-    def qkv_cols(x):  # this rank's query heads, key heads and value heads
-        q, k, v = x[:, :H * hd], x[:, H * hd:(H + KV) * hd], x[:, (H + KV) * hd:]
-        return torch.cat([part(q, 1), part(k, 1), part(v, 1)], 1)
+    def mine(name):
+        kept = tp_keep(name, full, r, n) if tp else None
+        if kept is None:
+            return None
+        axis, idx = kept
+        index = torch.from_numpy(idx).to(rt.device)
+        return lambda x: x.index_select(axis, index)
 
     ones = lambda m: Tensor.of(rt, np.ones((1, m), np.float32))
     w = {}
     for l in range(full.layers):
         pre = f"layers.{l}."
         w[pre + "input_layernorm"], w[pre + "post_attention_layernorm"] = ones(d), ones(d)
-        w[pre + "qkv_proj"] = keep(pre + "qkv_proj", draw(d, (H + 2 * KV) * hd), qkv_cols if tp else None)
-        w[pre + "o_proj"] = keep(pre + "o_proj", draw(H * hd, d), (lambda x: part(x, 0)) if tp else None)
+        w[pre + "qkv_proj"] = keep(pre + "qkv_proj", draw(d, (H + 2 * KV) * hd), mine(pre + "qkv_proj"))
+        w[pre + "o_proj"] = keep(pre + "o_proj", draw(H * hd, d), mine(pre + "o_proj"))
         if full.qk_norm:
             w[pre + "qk_norm"] = Tensor.of(rt, np.ones((c.heads + c.kv, 1, hd), np.float32))
         if full.experts:
@@ -299,12 +321,12 @@ def random_weights(rt, c, prec=None, seed=0, scale=0.02, full=None):
             w[pre + "experts.gate_up"] = keep(pre + "experts.gate_up", draw(full.experts, d, 2 * full.moe))
             w[pre + "experts.down"] = keep(pre + "experts.down", draw(full.experts, full.moe, d))
         else:
-            w[pre + "gate_up_proj"] = keep(pre + "gate_up_proj", draw(d, 2 * full.ffn), (lambda x: part(x, 1, 2)) if tp else None)
-            w[pre + "down_proj"] = keep(pre + "down_proj", draw(full.ffn, d), (lambda x: part(x, 0)) if tp else None)
+            w[pre + "gate_up_proj"] = keep(pre + "gate_up_proj", draw(d, 2 * full.ffn), mine(pre + "gate_up_proj"))
+            w[pre + "down_proj"] = keep(pre + "down_proj", draw(full.ffn, d), mine(pre + "down_proj"))
     w["norm"] = ones(d)
     embed = draw(full.vocab, d)
     w["embed"] = Tensor(rt, full.vocab, d, buf=embed.view(1, full.vocab, d))
-    w["embed.T"] = keep("embed.T", embed.t(), (lambda x: part(x, 1)) if tp else (lambda x: x))
+    w["embed.T"] = keep("embed.T", embed.t(), mine("embed.T") or (lambda x: x))
     cos, sin = rotary(full, full.places)
     w["cos"], w["sin"] = Tensor.of(rt, cos), Tensor.of(rt, sin)
     w["_blocks"] = [block(w, f"layers.{l}.") for l in range(full.layers)]

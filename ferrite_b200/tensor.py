@@ -865,7 +865,7 @@ def jit(f):
             inputs = [x.realize() for x in xs]
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):  # (other threads, NCCL's watchdog, may touch CUDA meanwhile)
                 out = f(*inputs).realize()
             graph.replay()
             state.update(inputs=inputs, graph=graph, out=out)

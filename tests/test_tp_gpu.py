@@ -1,0 +1,69 @@
+"""Tensor parallelism on two GPUs: the ranks' sharded decoder (NCCL all-reduce after o_proj and down_proj, sharded
+vocabulary pick) must give the single-GPU decoder's tokens and logits.  Skipped on a box with one GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, result):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from ferrite_b200 import llama
+    from ferrite_b200.tensor import Runtime, Tensor, jit
+    rt = Runtime(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=rt.device)
+    full = llama.model(dim=512, heads=8, kv=4, layers=2, vocab=1024, ffn=1024, eps=1e-5, theta=10000.0, places=64)
+    prec = llama.precision(full, "bfp8")
+    c = llama.tensor_parallel(full, rank, world, dist.group.WORLD)
+    w = llama.random_weights(rt, c, prec, seed=5, full=full, scale=0.05)
+    S, part = 4, 32
+    on = lambda row: Tensor.of(rt, [row], "int32")
+    kv = llama.kv_cache(c, S * part, llama.zeros(rt))
+    step = jit(lambda ids, places: llama.next_tokens(llama.forward(ids, places, w, c, kv, S), c))
+    ids, picks = [3, 500, 77, 1000], []
+    for i in range(5):
+        out = step(on(ids), on([i] * S))
+        ids = out.numpy().reshape(-1).tolist()
+        picks.append(ids)
+    if rank == 0:  # the same model on one GPU
+        full.vocab_shard = full.vocab
+        w1 = llama.random_weights(rt, full, prec, seed=5, scale=0.05)
+        kv1 = llama.kv_cache(full, S * part, llama.zeros(rt))
+        step1 = jit(lambda ids, places: llama.forward(ids, places, w1, full, kv1, S))
+        ids, agree, worst = [3, 500, 77, 1000], 0, 0.0
+        for i in range(5):
+            logits = step1(on(ids), on([i] * S)).numpy()[0]
+            for u in range(S):  # the ranks' pick is the best logit, or one a bf16 rounding apart from it
+                worst = max(worst, float(logits[u].max() - logits[u][picks[i][u]]) / float(np.ptp(logits[u])))
+            agree += sum(int(logits[u].argmax()) == picks[i][u] for u in range(S))
+            ids = picks[i]  # teacher-forced with the ranks' picks
+        result.put((agree, worst))
+        import time
+        time.sleep(1)  # let the queue's feeder thread send before the hard exit
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)  # (no NCCL teardown: the recorded graphs still hold its kernels)
+
+
+def test_two_gpus_decode_like_one(cuda):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    agree, worst = result.get(timeout=5)
+    assert worst < 0.01 and agree >= 18, (agree, worst)

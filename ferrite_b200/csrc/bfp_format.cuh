@@ -1,10 +1,4 @@
 // Packed block-float layout (see include/ferrite_b200.h) and the in-register unpack to bf16 pairs.
-//
-// The unpack never converts integers to floats one at a time.  A magnitude is OR-ed into the mantissa
-// of the bf16 constant 128.0 (0x4300), which makes the number 128 + mag exactly; one packed bf16x2 FMA
-// then computes (128 + mag) * scale - 128 * scale = mag * scale for two values at once.  The scale is a
-// power of two, so every step is exact and the result is the block float's value bit for bit
-// (models/gpt2.py:31-32 of the reference: +-mag * 2^(top-133)).
 #pragma once
 #include "common.cuh"
 
@@ -32,70 +26,67 @@ __host__ __device__ inline int64_t exp_offset(int fmt, int64_t K, int64_t b, int
   return unit_offset(fmt, K, b, k) + unit_mant_bytes(fmt) + (b % GROUP_RUNS) * KSTEP + k % KSTEP;
 }
 
-// Where a bfp4 value sits inside the 8 bytes of its (row, column block): column j of 16 is nibble
-// p of word h with j = 8h + 2*(p%4) + p/4, so that masking a word with 0x000F000F yields two neighbouring
-// columns in the two halves of a register.
+// Where a value sits in its run's bytes.  A magnitude and ITS OWN sign do not share a byte (or nibble): the sign is
+// parked one byte (three nibbles) further up, cyclically, so that masking a word - or the word rotated - leaves two
+// values in the two halves of a register with each sign already on bit 15 / 31 and each magnitude on the low bits:
+//   bfp8, word h of a run = columns 4h..4h+3:  byte0 = mag(c0) | sign(c3)<<7,  byte1 = mag(c2) | sign(c0)<<7,
+//                                              byte2 = mag(c1) | sign(c2)<<7,  byte3 = mag(c3) | sign(c1)<<7
+//   bfp4, word h of a run = columns 8h..8h+7:  nibble p = mag3(v_p) | sign(v_(p-3 mod 8))<<3, v_p = column 2*(p%4) + p/4
 __host__ __device__ inline int bfp4_nibble_of_column(int j) {  // j in 0..7 -> p
   return (j >> 1) + ((j & 1) << 2);
 }
-
-// bf16 bit patterns of 2^(top-133) and of -(128 * 2^(top-133)), each in both halves of a register.
-struct Scale8 {
-  uint32_t s2, c2;
-};
-__device__ __forceinline__ Scale8 scale8(uint32_t top) {
-  uint32_t s = top >= 7 ? (top - 6) << 7 : 1u << top;  // below 2^-126 the scale is a bf16 denormal
-  uint32_t c = 0x8000u | ((top + 1) << 7);             // -(2^(top-126))
-  return {s * 0x10001u, c * 0x10001u};
-}
-// bfp4: value = (code - 8) * 2^(top-129): scale 2^(top-129) and -(136 * scale)
-__device__ __forceinline__ Scale8 scale4(uint32_t top) {
-  uint32_t s = top >= 3 ? (top - 2) << 7 : 1u << (top + 4);
-  uint32_t c = 0x8000u | ((top + 5) << 7) | 0x08u;  // -(2^(top-122) * 1.0625)
-  return {s * 0x10001u, c * 0x10001u};
+__host__ __device__ inline int bfp8_byte_of_column(int j) {  // j in 0..3 -> the byte that holds its magnitude
+  return j == 0 ? 0 : j == 1 ? 2 : j == 2 ? 1 : 3;
 }
 
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+// The unpack never converts integers to floats and never touches the sign.  A magnitude sitting in the mantissa
+// field of a bf16 whose exponent field is zero IS a number: the subnormal mag * 2^-133.  The block float's value is
+// +-mag * 2^(top-133) (models/gpt2.py:31-32), i.e. that subnormal times 2^top: two exact packed multiplications by
+// powers of two (2^126, then 2^(top-126); one would overflow bf16's exponent), two values per instruction, the sign bit
+// riding along.  Per four bfp8 values: two masks and one rotate on the integer pipe, four multiplies on the FMA pipe.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
+constexpr uint32_t TWO_126_X2 = 0x7E807E80u;
+// bf16 pair 2^(top-126) (bfp8) / 2^(top-122) (bfp4: its 3-bit magnitude stands 4 bits higher)
+__device__ __forceinline__ uint32_t scale8(uint32_t top) { return ((top + 1) << 7) * 0x10001u; }
+__device__ __forceinline__ uint32_t scale4(uint32_t top) { return ((top + 5) << 7) * 0x10001u; }
 
 // Four bfp8 bytes (columns j..j+3 of a run) -> two registers of bf16 pairs (j, j+1) and (j+2, j+3).
-__device__ __forceinline__ void unpack8_word(uint32_t w, Scale8 sc, uint32_t& lo, uint32_t& hi) {
-  uint32_t r0, r1, m, a;
-  asm("prmt.b32 %0, %1, %1, 0x9180;" : "=r"(r0) : "r"(w));  // [sign-fill(b1) b1 sign-fill(b0) b0]
-  asm("prmt.b32 %0, %1, %1, 0xB3A2;" : "=r"(r1) : "r"(w));  // [sign-fill(b3) b3 sign-fill(b2) b2]
-  asm("lop3.b32 %0, %1, 0x807F807F, 0x43004300, 0xEA;" : "=r"(m) : "r"(r0));  // +-(128 + mag)
-  asm("lop3.b32 %0, %1, 0x80008000, %2, 0x6A;" : "=r"(a) : "r"(r0), "r"(sc.c2));  // -+128*scale
-  lo = fma_bf16x2(m, sc.s2, a);
-  asm("lop3.b32 %0, %1, 0x807F807F, 0x43004300, 0xEA;" : "=r"(m) : "r"(r1));
-  asm("lop3.b32 %0, %1, 0x80008000, %2, 0x6A;" : "=r"(a) : "r"(r1), "r"(sc.c2));
-  hi = fma_bf16x2(m, sc.s2, a);
+__device__ __forceinline__ void unpack8_word(uint32_t w, uint32_t s2, uint32_t& lo, uint32_t& hi) {
+  uint32_t a, r, b;
+  asm("lop3.b32 %0, %1, 0x807F807F, 0, 0xC0;" : "=r"(a) : "r"(w));
+  asm("shf.r.wrap.b32 %0, %1, %1, 8;" : "=r"(r) : "r"(w));
+  asm("lop3.b32 %0, %1, 0x807F807F, 0, 0xC0;" : "=r"(b) : "r"(r));
+  lo = mul_bf16x2(mul_bf16x2(a, TWO_126_X2), s2);
+  hi = mul_bf16x2(mul_bf16x2(b, TWO_126_X2), s2);
 }
 
 // One bfp4 word (8 columns) -> four registers of bf16 pairs (0,1) (2,3) (4,5) (6,7).
-__device__ __forceinline__ void unpack4_word(uint32_t w, Scale8 sc, uint32_t out[4]) {
+__device__ __forceinline__ void unpack4_word(uint32_t w, uint32_t s2, uint32_t out[4]) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint32_t m;
-    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(m) : "r"(w >> (4 * i)));  // 128 + code
-    out[i] = fma_bf16x2(m, sc.s2, sc.c2);
+    uint32_t r = w, m;
+    if (i) asm("shf.r.wrap.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(w), "r"(4 * i));
+    asm("lop3.b32 %0, %1, 0x80078007, 0, 0xC0;" : "=r"(m) : "r"(r));
+    out[i] = mul_bf16x2(mul_bf16x2(m, TWO_126_X2), s2);
   }
 }
 
 // A whole run of 16 columns as eight bf16-pair registers (columns 2i, 2i+1 in register i).
 __device__ __forceinline__ void unpack_run8(uint4 raw, uint32_t top, uint32_t v[8]) {
-  Scale8 sc = scale8(top);
-  unpack8_word(raw.x, sc, v[0], v[1]);
-  unpack8_word(raw.y, sc, v[2], v[3]);
-  unpack8_word(raw.z, sc, v[4], v[5]);
-  unpack8_word(raw.w, sc, v[6], v[7]);
+  const uint32_t s2 = scale8(top);
+  unpack8_word(raw.x, s2, v[0], v[1]);
+  unpack8_word(raw.y, s2, v[2], v[3]);
+  unpack8_word(raw.z, s2, v[4], v[5]);
+  unpack8_word(raw.w, s2, v[6], v[7]);
 }
 __device__ __forceinline__ void unpack_run4(uint2 raw, uint32_t top, uint32_t v[8]) {
-  Scale8 sc = scale4(top);
-  unpack4_word(raw.x, sc, v);
-  unpack4_word(raw.y, sc, v + 4);
+  const uint32_t s2 = scale4(top);
+  unpack4_word(raw.x, s2, v);
+  unpack4_word(raw.y, s2, v + 4);
 }
 
 }  // namespace fb

@@ -5,8 +5,10 @@
 // the kernel stays bound by the HBM stream of packed weights, which it reads exactly once:
 //
 //   x producer   (1 thread)  TMA tiles [tokens x 64] of the (normalised) activations, 128B-swizzled     -> smem ring
-//   16 worker warps          packed bytes: 128-bit global loads issued three steps ahead (registers, no staging in
-//                            shared memory: its bandwidth is what the bf16 operand tiles need) -> bf16 pairs
+//   x producer (same thread) cp.async.bulk.prefetch.L2 of the packed weights ten steps ahead
+//   16 worker warps          in 4 teams, each taking every fourth step: packed bytes by 128-bit global loads into
+//                            registers that are refilled for the team's next step as soon as they are unpacked (no
+//                            staging in shared memory, whose bandwidth the bf16 operand tiles need) -> bf16 pairs
 //                            (bfp_format.cuh) -> MN-major 128B-swizzled A tiles
 //   MMA issuer   (1 thread)  8 x tcgen05.mma (K = 16 each) per 128 rows, accumulating in TMEM; tcgen05.commit frees slots
 //   epilogue (worker warps)  tcgen05.ld -> shared memory -> RMSNorm row scale, SwiGLU / residual, bf16 / fp32 store
@@ -33,7 +35,8 @@ constexpr int STEP_ROWS = STEP_UNITS * KSTEP;
 constexpr int WORKERS = 512;    // one CTA per SM (a kernel that allocates tensor memory gets the SM to itself)
 constexpr int WARP_MMA = 16, WARP_X = 17;
 constexpr int THREADS = 18 * 32;
-constexpr int AHEAD = 3;        // steps of K a worker's loads run ahead of its unpacking
+constexpr int TEAMS = 4;        // teams of worker warps, each unpacking every fourth step on its own
+constexpr int PREFETCH = 10;    // steps of K the L2 prefetch runs ahead
 constexpr int A_SLOT_BYTES = TILE_N * STEP_ROWS * 2;
 constexpr int MAX_STAGES = 8;
 constexpr int WS_RSTD = 1024;  // workspace: row scales, then the normalised activations
@@ -91,7 +94,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   uint8_t* sA = smem;  // A slots; reused as the split-K exchange buffer once the MMAs are done
   const int x_slot_bytes = STEP_UNITS * nt * 128;  // a [tokens x 64] tile per 64 rows of K
   uint8_t* sX = sA + SA * A_SLOT_BYTES;
-  uint2* lut = reinterpret_cast<uint2*>(sX + SX * x_slot_bytes);  // exponent byte -> {scale, -offset * scale} bf16 pairs
+  uint32_t* lut = reinterpret_cast<uint32_t*>(sX + SX * x_slot_bytes);  // exponent byte -> its power of two as a bf16 pair
   uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 256);
   uint64_t* x_full = bars, *x_empty = bars + MAX_STAGES, *a_full = bars + 2 * MAX_STAGES, *a_empty = bars + 3 * MAX_STAGES;
   uint64_t* acc_full = bars + 4 * MAX_STAGES;
@@ -119,14 +122,13 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   }
   if (tid == 0) {
     for (int s = 0; s < SX; ++s) mbar_init(smem_u32(x_full + s), 1), mbar_init(smem_u32(x_empty + s), 1);
-    for (int s = 0; s < SA; ++s) mbar_init(smem_u32(a_full + s), WORKERS / 32), mbar_init(smem_u32(a_empty + s), 1);
+    for (int s = 0; s < SA; ++s) mbar_init(smem_u32(a_full + s), WORKERS / 32 / TEAMS), mbar_init(smem_u32(a_empty + s), 1);
     mbar_init(smem_u32(acc_full), 1);
     tmem_slot[1] = 0;
     fence_barrier_init();
   }
   if (tid < 256) {
-    const Scale8 sc = FMT == FB_BFP8 ? scale8(tid) : scale4(tid);
-    lut[tid] = make_uint2(sc.s2, sc.c2);
+    lut[tid] = FMT == FB_BFP8 ? scale8(tid) : scale4(tid);
   }
   if (warp == WARP_MMA) tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
   tc_fence_before();
@@ -148,7 +150,20 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     Ring rx;
     int ks = s0 % S, slot = s0 / S;
     const int y = p.mode == 1 ? (int)(zslot * p.x_slot_rows) : 0;
+    // The packed weights are pulled into L2 PREFETCH steps ahead of the workers' loads, so those find them at L2
+    // latency: a handful of loads in flight per thread then covers the HBM stream (no staging, no registers).
+    const uint8_t* Wp = static_cast<const uint8_t*>(a.W) + (p.mode == 1 ? expert * p.expert_bytes : 0);
+    auto prefetch = [&](int step) {
+      if (p.mode == 2 || step >= n_steps) return;
+      const int64_t first = (int64_t)(s0 + step) * STEP_UNITS;
+      const int units = min((int64_t)STEP_UNITS, KS - first);
+      if (units <= 0) return;
+      bulk_prefetch_l2(Wp + (g0 * KS + first) * UNIT, units * UNIT);
+      if (has_g1) bulk_prefetch_l2(Wp + (g1 * KS + first) * UNIT, units * UNIT);
+    };
+    for (int i = 0; i < PREFETCH; ++i) prefetch(i);
     for (int i = 0; i < n_steps; ++i, rx.next(SX)) {
+      prefetch(i + PREFETCH);
       const int s = rx.slot;
       mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
       mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
@@ -179,91 +194,79 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     }
     umma_commit(smem_u32(acc_full));
   } else if (warp < WORKERS / 32) {
-    // this thread's two (run, row) places in every 128-row step: where their bytes lie in the step's units of the
-    // packed matrix, and where their 16 columns go in the A slot
+    // The worker warps form TEAMS teams; team t unpacks steps t, t + TEAMS, ... on its own, so a warp synchronises
+    // (slot wait, proxy fence, arrive) once per 8 runs of 16 values instead of once per 2, and while one team waits
+    // for its loads the others unpack.  A thread owns one row k of the step and walks the tile's 8 runs.
+    constexpr int TEAM_THREADS = WORKERS / TEAMS;
+    const int team = tid / TEAM_THREADS, k = tid % TEAM_THREADS;  // TEAM_THREADS == STEP_ROWS
     const uint8_t* W = static_cast<const uint8_t*>(a.W) + (p.mode == 1 ? expert * p.expert_bytes : 0);
-    int64_t src[2];
-    uint32_t exp_rel[2], a_off[2][2];
-    bool col_ok[2];
-    int unit_of[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int u = tid + WORKERS * j, run8 = u >> 7, k = u & 127, grp = run8 >> 2, run = run8 & 3;
-      const int unit = k >> 6, ku = k & 63;
-      unit_of[j] = unit;
-      col_ok[j] = grp == 0 || has_g1;
-      src[j] = ((grp ? g1 : g0) * KS + unit) * UNIT + (run * KSTEP + ku) * RUN;
-      exp_rel[j] = UNIT_MANT + run * KSTEP + ku - (run * KSTEP + ku) * RUN;
-      const int slot = swiglu ? (run << 1 | grp) : run8;  // gate and up runs alternate: rows r and r + 16 pair up
-      const uint32_t row = ((k >> 3) * 2 + (slot >> 2)) * 1024 + (k & 7) * 128;
-      const int c = (slot & 3) * 2;
-      a_off[j][0] = row + ((c ^ (k & 7)) << 4);
-      a_off[j][1] = row + (((c + 1) ^ (k & 7)) << 4);
-    }
+    const int unit = k >> 6, ku = k & 63;
     using RawT = typename std::conditional<FMT == FB_BFP8, uint4, uint2>::type;
-    RawT q[AHEAD][2];
-    uint32_t top[AHEAD][2];
-    // the loads' own walk through the steps (they run AHEAD of the unpacking): rows f_ks * 128.. of slot f_slot
-    int f_ks = s0 % S, f_slot = s0 / S;
-    const uint8_t* f_w = W;  // the slot's expert's matrix, null if it picks none
-    auto pick = [&]() {
-      if (p.mode != 2) return;
-      const int e = f_slot < p.n_slots ? p.index[f_slot] : -1;
-      f_w = e >= 0 && e < p.n_experts ? static_cast<const uint8_t*>(a.W) + e * p.expert_bytes : nullptr;
-    };
-    pick();
-    auto fetch = [&](int step, int buf) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const bool ok = col_ok[j] && step < n_steps && f_w != nullptr && f_ks * STEP_UNITS + unit_of[j] < units_total;
-        const uint8_t* at = f_w + src[j] + (int64_t)f_ks * (STEP_UNITS * UNIT);
-        if (ok) {
-          q[buf][j] = __ldg(reinterpret_cast<const RawT*>(at));
-          top[buf][j] = __ldg(at + exp_rel[j]);
-        } else {  // past the end of K, or a column group past N: zeros
-          q[buf][j] = RawT{};
-          if (FMT == FB_BFP4) q[buf][j].x = 0x88888888u, q[buf][j].y = 0x88888888u;
-          top[buf][j] = 0;
-        }
-      }
-      if (++f_ks == S) f_ks = 0, ++f_slot, pick();
-    };
-#pragma unroll
-    for (int d = 0; d < AHEAD; ++d) fetch(d, d);
     const uint32_t sA32 = smem_u32(sA), lut32 = smem_u32(lut);
+    const uint32_t row_base = (uint32_t)((k >> 3) * 2 * 1024 + (k & 7) * 128);
     Ring ra;
-    for (int i0 = 0; i0 < n_steps; i0 += AHEAD) {
-#pragma unroll
-      for (int d = 0; d < AHEAD; ++d) {  // (buffers indexed by constants: they stay in registers)
-        const int i = i0 + d;
-        if (i < n_steps) {
-          const int sa = ra.slot;
-          mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
-          const uint32_t slot = sA32 + sa * A_SLOT_BYTES;
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const uint2 sc2 = ld_shared_v2(lut32 + top[d][j] * 8);
-            const Scale8 sc{sc2.x, sc2.y};
-            uint32_t v[8];
-            if constexpr (FMT == FB_BFP8) {
-              unpack8_word(q[d][j].x, sc, v[0], v[1]);
-              unpack8_word(q[d][j].y, sc, v[2], v[3]);
-              unpack8_word(q[d][j].z, sc, v[4], v[5]);
-              unpack8_word(q[d][j].w, sc, v[6], v[7]);
-            } else {
-              unpack4_word(q[d][j].x, sc, v);
-              unpack4_word(q[d][j].y, sc, v + 4);
-            }
-            st_shared_v4(slot + a_off[j][0], v[0], v[1], v[2], v[3]);
-            st_shared_v4(slot + a_off[j][1], v[4], v[5], v[6], v[7]);
-          }
-          fetch(i + AHEAD, d);
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
-          ra.next(SA);
-        }
+    for (int t = 0; t < team; ++t) ra.next(SA);
+    RawT q[8];
+    uint32_t top[8];
+    // where step i's bytes lie: its expert's matrix (mode 2), its 128 rows of K; null past the end or with no expert
+    auto rows_of = [&](int i) -> const uint8_t* {
+      if (i >= n_steps) return nullptr;
+      const int gs = s0 + i, slot_i = gs / S, ks = gs - slot_i * S;
+      const uint8_t* w = W;
+      if (p.mode == 2) {
+        const int e = p.index[slot_i];
+        if (e < 0 || e >= p.n_experts) return nullptr;
+        w = static_cast<const uint8_t*>(a.W) + e * p.expert_bytes;
       }
+      if (ks * STEP_UNITS + unit >= units_total) return nullptr;
+      return w + ((int64_t)ks * STEP_UNITS + unit) * UNIT;
+    };
+    auto load = [&](const uint8_t* rows, int j) {  // run j of the tile: group j / 4, run j % 4 of it
+      const int grp = j >> 2, run = j & 3;
+      if (rows != nullptr && (grp == 0 || has_g1)) {
+        const uint8_t* at = rows + (grp ? g1 : g0) * KS * UNIT;
+        q[j] = __ldg(reinterpret_cast<const RawT*>(at + (run * KSTEP + ku) * RUN));
+        top[j] = __ldg(at + UNIT_MANT + run * KSTEP + ku);
+      } else {  // past the end of K, a column group past N, or no expert: zeros
+        q[j] = RawT{};
+        top[j] = 0;
+      }
+    };
+    {
+      const uint8_t* rows = rows_of(team);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) load(rows, j);
+    }
+    const uint32_t k7 = (uint32_t)(k & 7);  // 16-byte chunk c of this thread's row goes to chunk c ^ k7 of its swizzled line
+    for (int i = team; i < n_steps; i += TEAMS) {
+      const uint8_t* next = rows_of(i + TEAMS);
+      const int sa = ra.slot;
+      mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
+      const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t sc = ld_shared_u32(lut32 + top[j] * 4);
+        uint32_t v[8];
+        if constexpr (FMT == FB_BFP8) {
+          unpack8_word(q[j].x, sc, v[0], v[1]);
+          unpack8_word(q[j].y, sc, v[2], v[3]);
+          unpack8_word(q[j].z, sc, v[4], v[5]);
+          unpack8_word(q[j].w, sc, v[6], v[7]);
+        } else {
+          unpack4_word(q[j].x, sc, v);
+          unpack4_word(q[j].y, sc, v + 4);
+        }
+        load(next, j);  // this register's next bytes are on their way while the rest of the step is unpacked
+        const int sl = swiglu ? ((j & 3) << 1 | j >> 2) : j;  // gate and up runs alternate: rows r and r + 16 pair up
+        const uint32_t at = slot + (sl >> 2) * 1024;
+        const uint32_t c0 = (uint32_t)(sl & 3) * 2;
+        st_shared_v4(at + ((c0 ^ k7) << 4), v[0], v[1], v[2], v[3]);
+        st_shared_v4(at + (((c0 + 1) ^ k7) << 4), v[4], v[5], v[6], v[7]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+      for (int t = 0; t < TEAMS; ++t) ra.next(SA);
     }
   }
 
@@ -418,8 +421,8 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots
   }
   pl.splits = best;
   pl.sps = (int)ceil_div(pl.steps, best);
-  pl.a_slots = pl.nt <= 64 ? 4 : 3;
-  pl.x_slots = pl.nt <= 64 ? 4 : 3;
+  pl.a_slots = pl.nt <= 64 ? 5 : 4;  // the teams' steps in flight, and one the tensor core reads
+  pl.x_slots = pl.nt <= 32 ? 4 : pl.nt <= 64 ? 3 : 2;
   pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 2048 + 5 * MAX_STAGES * 8 + 64;
   return pl;
 }

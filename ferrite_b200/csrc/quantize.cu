@@ -39,8 +39,9 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
       uint32_t e = (bits[j] >> 7) & 255u, m = (bits[j] & 127u) | (e ? 128u : 0u);
       uint32_t shift = min(top - e, 8u);
       uint32_t q = min((m + (1u << shift)) >> (shift + 1), 127u);
-      uint32_t byte = q ? (((bits[j] >> 15) << 7) | q) : 0u;  // a zero carries no sign
-      out[j >> 2] |= byte << (8 * (j & 3));
+      uint32_t sign = q ? bits[j] >> 15 : 0u;  // a zero carries no sign
+      const int at = bfp8_byte_of_column(j & 3);  // the magnitude's byte; the sign goes on top of the next byte up
+      out[j >> 2] |= (q << (8 * at)) | (sign << (8 * ((at + 1) & 3) + 7));
     }
     *reinterpret_cast<uint4*>(base + mant_offset(FMT, K, b, k)) = make_uint4(out[0], out[1], out[2], out[3]);
   } else {
@@ -50,8 +51,9 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
       uint32_t e = (bits[j] >> 7) & 255u, m = (bits[j] & 127u) | (e ? 128u : 0u);
       uint32_t shift = min(top - e, 8u);
       uint32_t q = shift < 4 ? min((m + (16u << shift)) >> (shift + 5), 7u) : 0u;
-      uint32_t code = (bits[j] >> 15) ? 8u - q : 8u + q;
-      out[j >> 3] |= code << (4 * bfp4_nibble_of_column(j & 7));
+      uint32_t sign = q ? bits[j] >> 15 : 0u;
+      const int at = bfp4_nibble_of_column(j & 7);  // the magnitude's nibble; the sign tops the nibble three up
+      out[j >> 3] |= (q << (4 * at)) | (sign << (4 * ((at + 3) & 7) + 3));
     }
     *reinterpret_cast<uint2*>(base + mant_offset(FMT, K, b, k)) = make_uint2(out[0], out[1]);
   }
@@ -61,12 +63,13 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
 template <int FMT>
 __device__ __forceinline__ void read_field(const uint8_t* base, int64_t K, int64_t b, int64_t k, int j, uint32_t& sign, uint32_t& mag) {
   if (FMT == FB_BFP8) {
-    uint32_t byte = base[mant_offset(FMT, K, b, k) + j];
-    sign = byte >> 7, mag = byte & 127u;
+    const uint32_t w = reinterpret_cast<const uint32_t*>(base + mant_offset(FMT, K, b, k))[j >> 2];
+    const int at = bfp8_byte_of_column(j & 3);
+    mag = (w >> (8 * at)) & 127u, sign = (w >> (8 * ((at + 1) & 3) + 7)) & 1u;
   } else {
-    uint32_t w = reinterpret_cast<const uint32_t*>(base + mant_offset(FMT, K, b, k))[j >> 3];
-    int code = (int)((w >> (4 * bfp4_nibble_of_column(j & 7))) & 15u) - 8;
-    sign = code < 0, mag = (uint32_t)(code < 0 ? -code : code);
+    const uint32_t w = reinterpret_cast<const uint32_t*>(base + mant_offset(FMT, K, b, k))[j >> 3];
+    const int at = bfp4_nibble_of_column(j & 7);
+    mag = (w >> (4 * at)) & 7u, sign = (w >> (4 * ((at + 3) & 7) + 3)) & 1u;
   }
 }
 
@@ -137,8 +140,8 @@ extern "C" int fb_quantize(int fmt, const void* src, int64_t batch, int64_t K, i
   int64_t total = batch * K * (N / 16);
   dim3 grid((unsigned)fb::ceil_div(total, 256)), block(256);
   auto s = (cudaStream_t)stream;
-  if (K % fb::KSTEP || N % (16 * fb::GROUP_RUNS)) {  // the padding of the last units holds zeros (bfp4's zero is the code 8)
-    if (cudaMemsetAsync(dst, fmt == FB_BFP8 ? 0 : 0x88, (size_t)batch * fb::packed_bytes(fmt, K, N), s) != cudaSuccess)
+  if (K % fb::KSTEP || N % (16 * fb::GROUP_RUNS)) {  // the padding of the last units holds zeros
+    if (cudaMemsetAsync(dst, 0, (size_t)batch * fb::packed_bytes(fmt, K, N), s) != cudaSuccess)
       return fb::launch_status("fb_quantize (padding)");
   }
   if (fmt == FB_BFP8) fb::quantize_kernel<FB_BFP8><<<grid, block, 0, s>>>((const uint16_t*)src, (uint8_t*)dst, batch, K, N);

@@ -30,10 +30,15 @@
  *     the units of one column group follow each other along K, so a stretch of K of one
  *     group is one contiguous piece of memory;
  *     inside a unit, for run r = (n/16)%4 and row i = k%64:
- *       mantissas  bfp8: 16 bytes at (r*64 + i)*16, byte j = sign<<7 | mag for column 16*(n/16) + j;
- *                  bfp4:  8 bytes at (r*64 + i)*8 read as two little-endian 32-bit words;
- *                         nibble p (bits 4p..4p+3) of word h holds column 8h + 2*(p%4) + p/4
- *                         of the run as the excess-8 code 8 + (sign ? -mag : mag);
+ *       mantissas  bfp8: 16 bytes at (r*64 + i)*16, four little-endian 32-bit words of four columns each;
+ *                         in word h (columns c0..c3 = 4h..4h+3 of the run):
+ *                           byte0 = mag(c0) | sign(c3)<<7   byte1 = mag(c2) | sign(c0)<<7
+ *                           byte2 = mag(c1) | sign(c2)<<7   byte3 = mag(c3) | sign(c1)<<7
+ *                  bfp4:  8 bytes at (r*64 + i)*8, two words of eight columns each; nibble p (bits 4p..4p+3)
+ *                         = mag3(v_p) | sign(v_((p+5) mod 8))<<3 with v_p = column 2*(p%4) + p/4 of the word.
+ *                  (A value's sign is parked one byte / three nibbles above its magnitude, cyclically, so a mask of
+ *                  the word, or of the word rotated, is two bf16 subnormals mag * 2^-133 with their signs in place;
+ *                  two exact multiplications by powers of two then give +-mag * 2^(top-133).)
  *       exponents  one byte at 4*64*(16|8) + r*64 + i.
  *   A zero magnitude is stored without a sign (as ferrite stores it).  fb_unpack_fields
  *   returns (top, sign, mag) per value for checking against the reference model.

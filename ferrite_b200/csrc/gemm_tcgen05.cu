@@ -10,7 +10,9 @@
 //                            registers that are refilled for the team's next step as soon as they are unpacked (no
 //                            staging in shared memory, whose bandwidth the bf16 operand tiles need) -> bf16 pairs
 //                            (bfp_format.cuh) -> MN-major 128B-swizzled A tiles
-//   MMA issuer   (1 thread)  8 x tcgen05.mma (K = 16 each) per 128 rows, accumulating in TMEM; tcgen05.commit frees slots
+//   2 MMA issuers (1 thread each) 8 x tcgen05.mma (K = 16 each) per 128 rows; one takes the even steps, the other the
+//                            odd ones, each into its own TMEM accumulator, so that one thread's barrier waits and
+//                            descriptor arithmetic hide behind the other's MMAs; tcgen05.commit frees the slots
 //   epilogue (worker warps)  tcgen05.ld -> shared memory -> RMSNorm row scale, SwiGLU / residual, bf16 / fp32 store
 //
 // Few column tiles (N = 4096 gives 32) cannot fill 148 SMs, so K is split across the CTAs of a thread-block cluster
@@ -33,8 +35,8 @@ constexpr int TILE_N = 128;     // output columns per CTA (MMA M): two 64-column
 constexpr int STEP_UNITS = 2;   // 64-row units of K per pipeline step: 128 rows
 constexpr int STEP_ROWS = STEP_UNITS * KSTEP;
 constexpr int WORKERS = 512;    // one CTA per SM (a kernel that allocates tensor memory gets the SM to itself)
-constexpr int WARP_MMA = 16, WARP_X = 17;
-constexpr int THREADS = 18 * 32;
+constexpr int WARP_MMA = 16, WARP_X = 18;  // warps 16 and 17 issue MMAs
+constexpr int THREADS = 19 * 32;
 constexpr int TEAMS = 4;        // teams of worker warps, each unpacking every fourth step on its own
 constexpr int PREFETCH = 10;    // steps of K the L2 prefetch runs ahead
 constexpr int A_SLOT_BYTES = TILE_N * STEP_ROWS * 2;
@@ -73,10 +75,14 @@ __device__ __forceinline__ void cluster_sync() {  // every thread of every CTA o
   __syncwarp();
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void store_remote_f32(uint32_t local_addr, uint32_t rank, float v) {
+// the address, in the cluster's shared window, of CTA `rank`'s copy of a shared-memory location of this CTA
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  return remote;
+}
+__device__ __forceinline__ void store_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
 template <int FMT>
@@ -95,7 +101,9 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   const int x_slot_bytes = STEP_UNITS * nt * 128;  // a [tokens x 64] tile per 64 rows of K
   uint8_t* sX = sA + SA * A_SLOT_BYTES;
   uint32_t* lut = reinterpret_cast<uint32_t*>(sX + SX * x_slot_bytes);  // exponent byte -> its power of two as a bf16 pair
-  uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 256);
+  float* tok_rstd = reinterpret_cast<float*>(lut + 256);  // per token: the RMSNorm row scale, the mixture's weight (or ones)
+  float* tok_scale = tok_rstd + 128;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tok_scale + 128);
   uint64_t* x_full = bars, *x_empty = bars + MAX_STAGES, *a_full = bars + 2 * MAX_STAGES, *a_empty = bars + 3 * MAX_STAGES;
   uint64_t* acc_full = bars + 4 * MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
@@ -123,7 +131,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   if (tid == 0) {
     for (int s = 0; s < SX; ++s) mbar_init(smem_u32(x_full + s), 1), mbar_init(smem_u32(x_empty + s), 1);
     for (int s = 0; s < SA; ++s) mbar_init(smem_u32(a_full + s), WORKERS / 32 / TEAMS), mbar_init(smem_u32(a_empty + s), 1);
-    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_full), 2);
     tmem_slot[1] = 0;
     fence_barrier_init();
   }
@@ -146,7 +154,12 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
 
   // steps are numbered through the slots in mode 2: step gs is rows (gs % S) * 128.. of slot gs / S
   const int S = p.mode == 2 ? p.steps_per_slot : p.steps_total;
-  if (warp == WARP_X && lane == 0) {
+  if (warp == WARP_X && lane >= 16) {  // the epilogue's per-token factors, fetched while the matmul runs
+    for (int t = lane - 16; t < nt; t += 16) {
+      tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
+      tok_scale[t] = p.row_scale && t < a.M ? bf16_bits_to_float(p.row_scale[(int64_t)zslot * a.M + t]) : 1.f;
+    }
+  } else if (warp == WARP_X && lane <= PREFETCH) {
     Ring rx;
     int ks = s0 % S, slot = s0 / S;
     const int y = p.mode == 1 ? (int)(zslot * p.x_slot_rows) : 0;
@@ -161,9 +174,9 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       bulk_prefetch_l2(Wp + (g0 * KS + first) * UNIT, units * UNIT);
       if (has_g1) bulk_prefetch_l2(Wp + (g1 * KS + first) * UNIT, units * UNIT);
     };
-    for (int i = 0; i < PREFETCH; ++i) prefetch(i);
-    for (int i = 0; i < n_steps; ++i, rx.next(SX)) {
-      prefetch(i + PREFETCH);
+    if (lane == 0) prefetch_tensormap(&tmap_x);
+    else prefetch(lane - 1);  // the first steps' bytes, asked for by a lane each
+    for (int i = 0; lane == 0 && i < n_steps; ++i, rx.next(SX)) {
       const int s = rx.slot;
       mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
       mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
@@ -172,8 +185,10 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       for (int u = 0; u < STEP_UNITS; ++u)  // rows of K past the end read as zeros (or meet zeros in A)
         tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, x0 + u * KSTEP, y, smem_u32(x_full + s));
       if (++ks == S) ks = 0, ++slot;
+      prefetch(i + PREFETCH);
     }
-  } else if (warp == WARP_MMA && lane == 0) {
+  } else if ((warp == WARP_MMA || warp == WARP_MMA + 1) && lane == 0) {
+    const int me = warp - WARP_MMA;  // steps me, me + 2, ... into accumulator `me`
     const uint32_t idesc = umma_idesc_bf16(nt, true, false);
     // A: MN-major, 64-column swizzle atoms 1024 B apart, groups of 8 rows of K 2048 B apart; 16 rows of K per MMA
     // X: K-major, one 128-byte swizzled row per token, groups of 8 tokens 1024 B apart; 32 bytes of K per MMA
@@ -181,14 +196,16 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     const uint64_t da0 = umma_smem_desc(smem_u32(sA), 1024, 2048), dx0 = umma_smem_desc(smem_u32(sX), 16, 1024);
     const uint32_t x_slot16 = (uint32_t)x_slot_bytes >> 4, x_unit16 = (uint32_t)(nt * 128) >> 4;
     Ring ra, rx;
-    for (int i = 0; i < n_steps; ++i, ra.next(SA), rx.next(SX)) {
+    if (me) ra.next(SA), rx.next(SX);
+    const uint32_t acc = tmem + me * nt;
+    for (int i = me; i < n_steps; i += 2, ra.next(SA), ra.next(SA), rx.next(SX), rx.next(SX)) {
       mbar_wait(smem_u32(a_full + ra.slot), ra.phase, abort_flag, WAIT_A_FULL);
       mbar_wait(smem_u32(x_full + rx.slot), rx.phase, abort_flag, WAIT_X_FULL);
       tc_fence_after();
       const uint64_t da = da0 + (uint32_t)ra.slot * (A_SLOT_BYTES >> 4), dx = dx0 + (uint32_t)rx.slot * x_slot16;
 #pragma unroll
       for (int kk = 0; kk < STEP_ROWS / 16; ++kk)
-        umma_bf16(tmem, da + kk * (4096 >> 4), dx + (kk >> 2) * x_unit16 + (kk & 3) * (32 >> 4), idesc, (i | kk) != 0);
+        umma_bf16(acc, da + kk * (4096 >> 4), dx + (kk >> 2) * x_unit16 + (kk & 3) * (32 >> 4), idesc, (i - me) | kk);
       umma_commit(smem_u32(a_empty + ra.slot));
       umma_commit(smem_u32(x_empty + rx.slot));
     }
@@ -286,14 +303,21 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   if (worker && (warp >> 2) < col_groups) {
     const int q = warp & 3, ncol = nt / col_groups, col0 = (warp >> 2) * ncol, row = 32 * q + lane;
     const uint32_t owner = row / rows_per;
-    const uint32_t at = smem_u32(exchange) + (uint32_t)(((split * nt + col0) * rows_per + row % rows_per) * 4);
+    uint32_t at = smem_u32(exchange) + (uint32_t)(((split * nt + col0) * rows_per + row % rows_per) * 4);
+    if (splits > 1) at = map_to_rank(at, owner);  // (a CTA's window is contiguous: offsets carry over)
     for (int cb = 0; cb < ncol; cb += 8) {
       float v[8];
       tmem_ld8(tmem + ((uint32_t)(32 * q) << 16) + col0 + cb, v);
+      if (n_steps > 1) {  // the odd steps' accumulator
+        float w[8];
+        tmem_ld8(tmem + ((uint32_t)(32 * q) << 16) + nt + col0 + cb, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += w[e];
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t addr = at + (uint32_t)((cb + e) * rows_per * 4);
-        if (splits > 1) store_remote_f32(addr, owner, v[e]);
+        if (splits > 1) store_cluster_f32(addr, v[e]);
         else asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v[e]) : "memory");
       }
     }
@@ -308,6 +332,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     const int own = min(rows_per, TILE_N - split * rows_per);   // rows of the tile this CTA owns
     const int out_rows = swiglu ? own / 2 : own;  // SwiGLU: rows 32q..32q+15 are gates, the next 16 their ups
     const int total = out_rows * (int)min((int64_t)nt, M);
+    const uint32_t inv_rows = 0xFFFFFFFFu / (uint32_t)max(out_rows, 1) + 1;  // idx / out_rows == umulhi(idx, inv_rows) for idx < 2^14
     for (int base = tid; base < total; base += 4 * WORKERS) {
       float res[4];
 #pragma unroll
@@ -315,7 +340,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
         const int idx = base + e * WORKERS;
         res[e] = 0.f;
         if (idx < total && a.epilogue == FB_EPI_RESIDUAL) {
-          const int t = idx / out_rows, n = TILE_N * tile + split * rows_per + idx % out_rows;
+          const int t = (int)__umulhi((uint32_t)idx, inv_rows), n = TILE_N * tile + split * rows_per + (idx - t * out_rows);
           if (n < a.N) res[e] = bf16_bits_to_float(__ldg(static_cast<const uint16_t*>(a.residual) + t * a.ldr + n));
         }
       }
@@ -323,7 +348,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       for (int e = 0; e < 4; ++e) {
         const int idx = base + e * WORKERS;
         if (idx >= total) break;
-        const int t = idx / out_rows, o = idx % out_rows;
+        const int t = (int)__umulhi((uint32_t)idx, inv_rows), o = idx - t * out_rows;
         const int lr = swiglu ? (o / 16) * 32 + o % 16 : o;  // row inside this CTA's slice
         float val = 0.f, up = 0.f;
         for (int s = 0; s < splits; ++s) {
@@ -331,8 +356,8 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
           val += src[lr];
           if (swiglu) up += src[lr + 16];
         }
-        if (p.rstd) val *= p.rstd[t], up *= p.rstd[t];
-        const float scale = p.row_scale ? bf16_bits_to_float(p.row_scale[(int64_t)zslot * M + t]) : 1.f;
+        val *= tok_rstd[t], up *= tok_rstd[t];
+        const float scale = tok_scale[t];
         const int tr = split * rows_per + lr;  // row inside the tile
         int64_t n;
         if (swiglu) {
@@ -403,7 +428,7 @@ struct Plan {
 Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots = 1, int mode = 0) {
   Plan pl;
   pl.nt = (int)((M + 15) / 16 * 16);
-  pl.tmem_cols = pl.nt <= 32 ? 32 : pl.nt <= 64 ? 64 : 128;
+  pl.tmem_cols = pl.nt <= 16 ? 32 : pl.nt <= 32 ? 64 : pl.nt <= 64 ? 128 : 256;  // two accumulators
   pl.tiles = (int)(epilogue == FB_EPI_SWIGLU ? groups_of(N) / 2 : (groups_of(N) + 1) / 2);
   pl.steps = (int)ceil_div(K, STEP_ROWS) * (mode == 2 ? slots : 1);
   const int64_t ctas_per_split = (int64_t)pl.tiles * (mode == 1 ? slots : 1);
@@ -423,7 +448,7 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots
   pl.sps = (int)ceil_div(pl.steps, best);
   pl.a_slots = pl.nt <= 64 ? 5 : 4;  // the teams' steps in flight, and one the tensor core reads
   pl.x_slots = pl.nt <= 32 ? 4 : pl.nt <= 64 ? 3 : 2;
-  pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 2048 + 5 * MAX_STAGES * 8 + 64;
+  pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 2048 + 1024 + 5 * MAX_STAGES * 8 + 64;
   return pl;
 }
 

@@ -446,8 +446,12 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots
   }
   pl.splits = best;
   pl.sps = (int)ceil_div(pl.steps, best);
-  pl.a_slots = pl.nt <= 64 ? 5 : 4;  // the teams' steps in flight, and one the tensor core reads
-  pl.x_slots = pl.nt <= 32 ? 4 : pl.nt <= 64 ? 3 : 2;
+  // Both rings have an even number of slots, so a slot is always consumed by the same one of the two MMA issuers:
+  // a parity wait is only sound when the waiter knows that the phase before has completed, and an issuer knows that
+  // of the slots it has consumed itself.  (With five A slots the issuer of the odd steps could run a lap ahead of a
+  // late team and take the untouched barrier of step 0 for the finished one of step 5.)
+  pl.a_slots = TEAMS;  // each team refills its own slot while the tensor core reads the other teams'
+  pl.x_slots = pl.nt <= 64 ? 4 : 2;
   pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 2048 + 1024 + 5 * MAX_STAGES * 8 + 64;
   return pl;
 }

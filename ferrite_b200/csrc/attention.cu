@@ -64,6 +64,7 @@ __device__ __forceinline__ uint32_t tile_off(int r, int ch) { return (uint32_t)(
 
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs a) {
+  griddep_launch_dependents();
   constexpr int CH = HD / 8;               // 16-byte chunks per row
   constexpr int TILE_BYTES = KEY_TILE * HD * 2;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -239,6 +240,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
 // one block per (entry, row): weight each split by exp2(its max - the overall max), sum, divide
 template <int HD>
 __global__ void __launch_bounds__(HD) attention_combine_kernel(AttnArgs a) {
+  griddep_launch_dependents();
   const int e = blockIdx.x / a.rows, row = blockIdx.x % a.rows, d = threadIdx.x;
   const int e0 = e / a.E1, e1 = e % a.E1, tiles = (a.rows + 15) / 16;
   const int64_t first = (((int64_t)e * tiles + row / 16) * a.splits) * 16 + row % 16;

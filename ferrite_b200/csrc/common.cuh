@@ -48,4 +48,14 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may start while
+// the kernel before it in the stream still runs; it must call griddep_wait() before it reads anything that kernel
+// wrote (the call returns once that kernel has finished and its writes are visible).  Every kernel of the decode
+// step calls griddep_launch_dependents() first thing: it tells the scheduler that the next kernel in the stream may
+// be started as soon as room frees up (a no-op when that kernel was launched the ordinary way).
+#if defined(__CUDACC__)
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 }  // namespace fb

@@ -8,6 +8,7 @@ namespace fb {
 // out[t, :] = table[ids[t], :]  (Tensor.gather, ferrite/tensor.py:116-126; ferrite/compiler.py:1574-1580)
 __global__ void gather_rows_kernel(const uint4* __restrict__ table, const int32_t* __restrict__ ids, uint4* __restrict__ out,
                                    int64_t row_vecs, int64_t table_rows) {
+  griddep_launch_dependents();
   const int64_t t = blockIdx.x;
   int64_t id = ids[t];
   id = id < 0 ? 0 : id >= table_rows ? table_rows - 1 : id;  // nothing checks an id's bounds on ferrite; here it is clamped
@@ -36,6 +37,7 @@ struct RopeArgs {
 };
 
 __global__ void rope_kv_kernel(RopeArgs a) {
+  griddep_launch_dependents();
   const int t = blockIdx.x, h = blockIdx.y, half = a.hd / 2, d = threadIdx.x;  // blockDim.x == hd / 2
   const uint16_t* x = a.qkv + t * a.ld_qkv + (int64_t)h * a.hd;
   float x1 = bf16_bits_to_float(x[d]), x2 = bf16_bits_to_float(x[d + half]);
@@ -70,6 +72,7 @@ __global__ void rope_kv_kernel(RopeArgs a) {
 // out = x * rsqrt(mean(x^2) + eps) * w  (models/llama.py:82-85), one block per row
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict__ x, int64_t ldx, const uint16_t* __restrict__ w,
                                                       uint16_t* __restrict__ out, int64_t ldo, int64_t cols, float eps) {
+  griddep_launch_dependents();
   const int64_t t = blockIdx.x;
   float ss = 0.f;
   for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {

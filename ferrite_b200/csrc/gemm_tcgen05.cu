@@ -109,6 +109,11 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   const uint32_t abort_flag = smem_u32(tmem_slot + 1);
 
+  // The kernel is launched as a programmatic dependent of the kernel before it: everything up to a griddep_wait()
+  // (barriers, tensor memory, the first weight loads and their L2 prefetch - weights are never written by a kernel of
+  // the stream) overlaps that kernel's last CTAs; the activations, row scales, residual and expert index are read after.
+  griddep_launch_dependents();
+  if (p.mode != 0) griddep_wait();  // the expert index decides what is read at all
   // an indexed matmul's slot that picks no expert is zeros, with nothing read (ferrite/tensor.py:458-460)
   const int zslot = p.mode == 1 ? (int)blockIdx.z : 0;
   int expert = 0;
@@ -155,6 +160,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   // steps are numbered through the slots in mode 2: step gs is rows (gs % S) * 128.. of slot gs / S
   const int S = p.mode == 2 ? p.steps_per_slot : p.steps_total;
   if (warp == WARP_X && lane >= 16) {  // the epilogue's per-token factors, fetched while the matmul runs
+    griddep_wait();
     for (int t = lane - 16; t < nt; t += 16) {
       tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
       tok_scale[t] = p.row_scale && t < a.M ? bf16_bits_to_float(p.row_scale[(int64_t)zslot * a.M + t]) : 1.f;
@@ -176,6 +182,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
     };
     if (lane == 0) prefetch_tensormap(&tmap_x);
     else prefetch(lane - 1);  // the first steps' bytes, asked for by a lane each
+    if (lane == 0) griddep_wait();  // the activations come from the kernel before
     for (int i = 0; lane == 0 && i < n_steps; ++i, rx.next(SX)) {
       const int s = rx.slot;
       mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
@@ -328,6 +335,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
 
   // ---- epilogue over this CTA's rows: sum the splits in rank order, scale, SwiGLU / residual, store
   if (worker) {
+    griddep_wait();  // (long since true: the MMAs consumed that kernel's activations) - the residual is its output too
     const int64_t M = a.M;
     const int own = min(rows_per, TILE_N - split * rows_per);   // rows of the tile this CTA owns
     const int out_rows = swiglu ? own / 2 : own;  // SwiGLU: rows 32q..32q+15 are gates, the next 16 their ups
@@ -386,6 +394,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
 // The row scale commutes with the matmul, so the GEMM applies it to the accumulators.
 __global__ void __launch_bounds__(256) rms_prepare_kernel(const uint16_t* __restrict__ x, int64_t ldx, const uint16_t* __restrict__ g,
                                                           int64_t K, float eps, uint16_t* __restrict__ xn, float* __restrict__ rstd) {
+  griddep_launch_dependents();
   const int t = blockIdx.x;
   float ss = 0.f;
   for (int64_t k = 2 * threadIdx.x; k < K; k += 2 * blockDim.x) {
@@ -515,10 +524,12 @@ static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) 
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.tiles, pl.splits, mode == 1 ? slots : 1), cfg.blockDim = dim3(THREADS), cfg.dynamicSmemBytes = pl.smem, cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = pl.splits, attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the kernel before it drains
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 2;
   if (cudaLaunchKernelEx(&cfg, kernel, tmap, p) != cudaSuccess) return launch_status("fb_linear (tcgen05 launch)");
   return launch_status("fb_linear (tcgen05)");
 }

@@ -8,6 +8,7 @@ namespace fb {
 // take the gate's block, 4-7 the up's).  See gemv.cuh for the per-lane work.
 template <int FMT, int M, bool NORM>
 __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
+  griddep_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool swiglu = a.epilogue == FB_EPI_SWIGLU;
   const int G = swiglu ? 4 : 8;

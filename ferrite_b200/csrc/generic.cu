@@ -43,6 +43,7 @@ __device__ __forceinline__ float load_as_float(const EwOperand& o, int64_t b, in
 }
 
 __global__ void __launch_bounds__(256) elementwise_kernel(const __grid_constant__ EwArgs a) {
+  griddep_launch_dependents();
   const int64_t total = a.batch * a.rows * a.cols;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t c = i % a.cols, r = (i / a.cols) % a.rows, b = i / (a.cols * a.rows);

@@ -17,6 +17,7 @@ __device__ __forceinline__ float as_float<float>(float v) { return v; }
 template <typename T>
 __global__ void __launch_bounds__(256) topk_kernel(const T* __restrict__ x, int64_t ldx, int64_t cols, int k, const int32_t* __restrict__ labels,
                                                    T* __restrict__ values, int32_t* __restrict__ ids, uint16_t* __restrict__ weights, int64_t ldo) {
+  griddep_launch_dependents();
   const int64_t row = blockIdx.x;
   const T* xr = x + row * ldx;
   __shared__ float sv[8];
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(256) topk_kernel(const T* __restrict__ x, int6
 // One block: experts some row picks with a weight that is not zero, ascending, then n; and each entry's weight per row.
 __global__ void __launch_bounds__(256) touched_kernel(const int32_t* __restrict__ ids, const uint16_t* __restrict__ w, int64_t rows, int k, int n,
                                                       int slots, int32_t* __restrict__ experts, uint16_t* __restrict__ out) {
+  griddep_launch_dependents();
   extern __shared__ int32_t flag[];  // [n] then the compacted list [slots]
   int32_t* listed = flag + n;
   for (int e = threadIdx.x; e < n; e += blockDim.x) flag[e] = 0;

@@ -11,6 +11,7 @@ o_proj + residual, RMSNorm + gate_up + SwiGLU, down_proj + residual), final norm
     e2e        the same through the public call with host buffers: ids and places copied in from pinned memory and the
                picked tokens read back, every step
     roofline   the block-float matmul kernel (the dominant kernel): its algorithmic bytes over its measured duration
+    matmul_sweep  (1 GPU) the isolated matmul with fused RMSNorm and SwiGLU over M, N and both formats: GB/s and fraction of peak
     cpu_baseline / --impl reference: the numpy restatement of the reference's CPU path on this box's host cores, on a
                bounded sample (one block and the output layer, scaled to the model)
 """
@@ -254,6 +255,9 @@ def run_ferrite(args):
                           "frac_of_hbm": step_bytes(c, S, ctx + args.warmup + args.steps // 2) / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }
     if rank == 0 and world == 1:
+        del w, caches, step, mm
+        torch.cuda.empty_cache()
+        line["matmul_sweep"] = matmul_sweep(rt.device, peaks["hbm_gbs"])
         line["cpu_baseline"] = cpu_baseline(args, sample_seconds=20)
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -262,6 +266,45 @@ def run_ferrite(args):
         torch.cuda.synchronize()
         sys.stdout.flush()
         os._exit(0)
+
+
+def matmul_sweep(device, peak_gbs, calls=200):
+    """BASELINE.json configs[1]: the isolated block-float matmul, RMSNorm prologue and SwiGLU epilogue fused, K = 4096,
+    M in {1, 8, 32, 128}, N in {4096, 14336}, bfp8 and bfp4.  `calls` back-to-back calls (one recorded graph) rotate
+    through distinct weight buffers that together exceed L2 several times, so every call streams its matrix from HBM.
+    Algorithmic bytes per call: the packed matrix, the activations in, the result out, the norm's weight."""
+    import torch
+    from ferrite_b200 import ops
+    K, rows, gen = 4096, [], torch.Generator(device=device).manual_seed(0)
+    g = (1 + 0.1 * torch.randn(K, device=device, generator=gen)).bfloat16()
+    for fmt, per_value in (("bfp8", 1.0625), ("bfp4", 0.5625)):
+        for N in (4096, 14336):
+            copies = min(48, -(-(512 << 20) // int(K * N * per_value)))
+            ws = [ops.quantize((torch.randn(K, N, device=device, generator=gen) * 0.02).bfloat16(), fmt) for _ in range(copies)]
+            for M in (1, 8, 32, 128):
+                x = torch.randn(M, K, device=device, generator=gen).bfloat16()
+                out = torch.empty(M, N // 2, device=device, dtype=torch.bfloat16)
+                for i in range(3):
+                    ops.linear(x, ws[i % copies], out=out, norm_w=g, eps=1e-5, epilogue="swiglu")
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for i in range(calls):
+                        ops.linear(x, ws[i % copies], out=out, norm_w=g, eps=1e-5, epilogue="swiglu")
+                graph.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / calls
+                nbytes = K * N * per_value + 2 * M * K + 2 * M * (N // 2) + 2 * K
+                rows.append({"fmt": fmt, "M": M, "N": N, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
+                             "frac": round(nbytes / us / 1e3 / peak_gbs, 3)})
+            del ws
+            torch.cuda.empty_cache()
+    return {"what": "RMSNorm + [M,4096]x[4096,N] + SwiGLU, %d calls rotating weight copies > L2" % calls, "peak_GB/s": peak_gbs, "rows": rows}
 
 
 def cpu_sample(args, seconds):

@@ -307,7 +307,46 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   else __syncthreads();
   // worker warps sharing one quarter of the TMEM lanes split the token columns, in runs of whole 8-column loads
   const int col_groups = nt % 32 == 0 ? 4 : nt % 16 == 0 ? 2 : 1;
-  if (worker && (warp >> 2) < col_groups) {
+  if (splits == 1 && worker && (warp >> 2) < col_groups) {
+    // ---- no K split: the epilogue runs straight from tensor memory.  Lane = tile row = output column, so a warp's
+    // store of one token is 32 consecutive columns; SwiGLU's gate (lanes 0-15) meets its up (lanes 16-31) by a shuffle.
+    griddep_wait();  // (long since true: the MMAs consumed that kernel's activations) - the residual is its output too
+    const int q = warp & 3, ncol = nt / col_groups, col0 = (warp >> 2) * ncol, row = 32 * q + lane;
+    const int64_t n = swiglu ? 64 * (int64_t)tile + 16 * q + (lane & 15) : TILE_N * (int64_t)tile + row;
+    const bool live = swiglu ? lane < 16 && n < a.N / 2 : n < a.N;
+    for (int cb = 0; cb < ncol && col0 + cb < a.M; cb += 8) {
+      float v[8], res[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {  // the residual reads of the eight tokens are in flight together
+        const int t = col0 + cb + e;
+        res[e] = live && t < a.M && a.epilogue == FB_EPI_RESIDUAL
+                     ? bf16_bits_to_float(__ldg(static_cast<const uint16_t*>(a.residual) + t * a.ldr + n)) : 0.f;
+      }
+      tmem_ld8(tmem + ((uint32_t)(32 * q) << 16) + col0 + cb, v);
+      if (n_steps > 1) {  // the odd steps' accumulator
+        float w[8];
+        tmem_ld8(tmem + ((uint32_t)(32 * q) << 16) + nt + col0 + cb, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += w[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int t = col0 + cb + e;  // (the same for the whole warp)
+        if (t >= a.M) break;
+        float val = v[e] * tok_rstd[t];
+        if (swiglu) {
+          const float up = __shfl_down_sync(0xffffffffu, val, 16);
+          val = val / (1.f + __expf(-val)) * up * tok_scale[t];
+        } else {
+          val = val * tok_scale[t] + res[e];
+        }
+        if (!live) continue;
+        const int64_t at = zslot * p.out_slot_stride + t * a.ldo + n;
+        if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = val;
+        else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(val);
+      }
+    }
+  } else if (worker && (warp >> 2) < col_groups) {
     const int q = warp & 3, ncol = nt / col_groups, col0 = (warp >> 2) * ncol, row = 32 * q + lane;
     const uint32_t owner = row / rows_per;
     uint32_t at = smem_u32(exchange) + (uint32_t)(((split * nt + col0) * rows_per + row % rows_per) * 4);
@@ -331,10 +370,9 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   }
   tc_fence_before();
   if (splits > 1) cluster_sync();
-  else __syncthreads();
 
   // ---- epilogue over this CTA's rows: sum the splits in rank order, scale, SwiGLU / residual, store
-  if (worker) {
+  if (worker && splits > 1) {
     griddep_wait();  // (long since true: the MMAs consumed that kernel's activations) - the residual is its output too
     const int64_t M = a.M;
     const int own = min(rows_per, TILE_N - split * rows_per);   // rows of the tile this CTA owns
@@ -474,7 +512,7 @@ bool linear_tcgen05_supports(const LinearArgs& a) {
 
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N) {
   (void)N;
-  if (M <= 4) return 0;
+  if (M <= 1) return 0;
   return WS_RSTD + (size_t)(M < 128 ? M : 128) * K * 2;
 }
 

@@ -1,6 +1,7 @@
 // fb_linear for a few tokens: the block-float GEMV with RMSNorm prologue and SwiGLU / residual epilogue.
 #include "gemv.cuh"
 #include "linear.cuh"
+#include "sm100.cuh"
 
 namespace fb {
 
@@ -16,6 +17,13 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
   const int64_t NB = a.N / 16, K = a.K;
   const int64_t b = blockIdx.x + (grp ? NB / 2 : 0);
   const uint8_t* col = static_cast<const uint8_t*>(a.W) + (b / GROUP_RUNS) * ksteps_of(K) * unit_bytes(FMT);
+  // The CTAs of a column group's four runs read interleaved 1 KB pieces of one contiguous strip; the CTA of run 0 asks
+  // for the whole strip to be brought into L2 up front (the bulk path keeps far more bytes in flight than a CTA's
+  // loads can), so the loads below mostly find their bytes there.
+  if (b % GROUP_RUNS == 0 && wg == 0 && lane == 0) {
+    const int64_t bytes = ksteps_of(K) * unit_bytes(FMT);
+    for (int64_t at = 0; at < bytes; at += 32768) bulk_prefetch_l2(col + at, (uint32_t)(bytes - at < 32768 ? bytes - at : 32768));
+  }
 
   float acc[M][16], ss[M];
 #pragma unroll

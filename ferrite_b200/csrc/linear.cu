@@ -21,7 +21,8 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
              "fb_linear: misaligned pointer");
   fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, norm_w, eps, epilogue, residual, ldr, workspace, workspace_bytes};
   auto s = (cudaStream_t)stream;
-  if (M > 4 && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);
+  // one token: the CUDA-core GEMV; more: the tensor-core kernel, whose cost hardly grows with the tokens
+  if (M > 1 && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);
   return fb::linear_gemv(a, s);
 }
 

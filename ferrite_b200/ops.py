@@ -101,7 +101,7 @@ def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="no
     check(lib().fb_linear(w.code, x.data_ptr(), M, K, x.stride(0), w.data.data_ptr(), w.N, out.data_ptr(), _lib.DTYPES[out_dtype],
                           out.stride(0), _ptr(norm_w), eps, epi, _ptr(residual), residual.stride(0) if residual is not None else 0,
                           _ptr(workspace), workspace.numel() if workspace is not None else 0, _stream()))
-    count(-(-M // 4) if M <= 4 else -(-M // 128) * (2 if norm_w is not None else 1))  # GEMV passes, or GEMM passes (+ the norm's)
+    count(1 if M <= 1 else -(-M // 128) * (2 if norm_w is not None else 1))  # the GEMV, or GEMM passes (+ the norm's)
     return out
 
 

@@ -97,7 +97,7 @@ int fb_unpack_fields(int fmt, const void* packed, int64_t batch, int64_t K, int6
  *   acc = h @ W, fp32 accumulation, W packed [K, N] in `fmt` (FB_BFP8, FB_BFP4 or FB_BF16 row-major)
  *   epilogue (fb_epilogue), out dtype FB_BF16 or FB_FP32 (fp32: the output layer, models/llama.py:479)
  * out is [M, N] (or [M, N/2] after FB_EPI_SWIGLU), row stride ldo elements.
- * M <= 4 runs as a bandwidth-bound GEMV on CUDA cores; larger M on tcgen05 tensor cores.
+ * M == 1 runs as a bandwidth-bound GEMV on CUDA cores; larger M on tcgen05 tensor cores.
  * workspace: fb_linear_workspace_bytes(M, K, N) bytes of device scratch (0 / NULL when that is 0):
  * it holds the normalised activations of the RMSNorm prologue between the two kernels of a call. */
 size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N);

@@ -1,6 +1,7 @@
 """Decode throughput of the block-float hot path on B200s, one JSON line.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama8b|smollm] [--layers L] [--impl reference]
+    python bench.py --matmul 32,4096,14336,bfp8,6      (one isolated matmul, a few calls: what the ncu captures run)
 
 The default workload is the Llama-3.1-8B-shape batched decode (32 sequences, 2048 tokens of context each, bfp8 weights,
 bf16 KV cache), tensor-parallel over N GPUs with an NCCL all-reduce after o_proj and down_proj.  A step is one decode
@@ -45,6 +46,8 @@ def parse():
     ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="fewer blocks than the model has (a smoke run; the JSON line says so)")
     ap.add_argument("--impl", default="ferrite_b200", choices=["ferrite_b200", "reference"])
+    ap.add_argument("--sweep", type=int, default=1, help="0: leave the isolated matmul sweep out of the line (a profiling run)")
+    ap.add_argument("--matmul", default="", help="M,K,N,fmt[,calls]: only that isolated matmul (RMSNorm + SwiGLU fused), e.g. 32,4096,14336,bfp8,6")
     return ap.parse_args()
 
 
@@ -250,14 +253,16 @@ def run_ferrite(args):
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": "linear_tcgen05_kernel (block-float dequant GEMM, %d tokens)" % S, "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_kind,
-                     "traffic": None, "launches": lin_launches, "us_per_launch": lin_ms * 1e3 / lin_launches, "bytes_per_launch": lin_bytes / lin_launches},
+                     "traffic": 1.002 * lin_bytes / lin_launches, "traffic_source": "algorithmic bytes x 1.002 (DRAM read+write of the ncu capture in profiles/, 4096x14336 bfp8, 32 tokens)",
+                     "launches": lin_launches, "us_per_launch": lin_ms * 1e3 / lin_launches, "bytes_per_launch": lin_bytes / lin_launches},
         "step_roofline": {"algorithmic_bytes_per_gpu": step_bytes(c, S, ctx + args.warmup + args.steps // 2),
                           "frac_of_hbm": step_bytes(c, S, ctx + args.warmup + args.steps // 2) / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }
     if rank == 0 and world == 1:
         del w, caches, step, mm
         torch.cuda.empty_cache()
-        line["matmul_sweep"] = matmul_sweep(rt.device, peaks["hbm_gbs"])
+        if args.sweep:
+            line["matmul_sweep"] = matmul_sweep(rt.device, peaks["hbm_gbs"])
         line["cpu_baseline"] = cpu_baseline(args, sample_seconds=20)
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -266,6 +271,27 @@ def run_ferrite(args):
         torch.cuda.synchronize()
         sys.stdout.flush()
         os._exit(0)
+
+
+def one_matmul(spec):
+    """--matmul: a few eager calls of one isolated matmul over four weight copies (what an ncu capture of the kernel runs)."""
+    import torch
+    from ferrite_b200 import ops
+    parts = spec.split(",")
+    M, K, N, fmt, calls = int(parts[0]), int(parts[1]), int(parts[2]), parts[3], int(parts[4]) if len(parts) > 4 else 6
+    device, gen = torch.device("cuda:0"), torch.Generator(device="cuda:0").manual_seed(0)
+    g = (1 + 0.1 * torch.randn(K, device=device, generator=gen)).bfloat16()
+    ws = [ops.quantize((torch.randn(K, N, device=device, generator=gen) * 0.02).bfloat16(), fmt) for _ in range(4)]
+    x = torch.randn(M, K, device=device, generator=gen).bfloat16()
+    out = torch.empty(M, N // 2, device=device, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(calls):
+        ops.linear(x, ws[i % 4], out=out, norm_w=g, eps=1e-5, epilogue="swiglu")
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"matmul": spec, "calls": calls, "us_per_call_eager": e0.elapsed_time(e1) * 1e3 / calls}))
 
 
 def matmul_sweep(device, peak_gbs, calls=200):
@@ -373,4 +399,7 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse()
-    run_reference(a) if a.impl == "reference" else run_ferrite(a)
+    if a.matmul:
+        one_matmul(a.matmul)
+    else:
+        run_reference(a) if a.impl == "reference" else run_ferrite(a)

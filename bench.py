@@ -33,6 +33,14 @@ WORKLOADS = {
     "llama8b": dict(model=dict(dim=4096, heads=32, kv=8, layers=32, vocab=128256, ffn=14336, theta=500000.0, eps=1e-5), mode="bfp8",
                     sequences=32, context=2048, name="llama-3.1-8b-shape bfp8, 32 sequences x 2048 context, bf16 KV"),
     # BASELINE.json configs[0]: SmolLM-135M shape, batch 1 (the reference's own CPU-runnable case)
+    # BASELINE.json configs[3]: Mixtral-8x7B shape, attention bfp8, experts bfp4, 64 sequences x 1024 context (one GPU holds it)
+    "mixtral": dict(model=dict(dim=4096, heads=32, kv=8, layers=32, vocab=32000, ffn=0, experts=8, k=2, moe=14336, norm_topk=True, theta=1000000.0, eps=1e-5),
+                    mode="experts", sequences=64, context=1024, name="mixtral-8x7b-shape, attention bfp8 / experts bfp4, top-2 of 8, 64 sequences x 1024 context, bf16 KV"),
+    # BASELINE.json configs[4]: Qwen3-30B-A3B shape, bfp8, 128 sessions with contexts drawn uniformly from 256..8192 (seeded)
+    "qwen3moe": dict(model=dict(dim=2048, heads=32, kv=4, head_dim=128, layers=48, vocab=151936, ffn=0, experts=128, k=8, moe=768, norm_topk=True, qk_norm=True,
+                                theta=1000000.0, eps=1e-6),
+                     mode="bfp8", sequences=128, context=8192, ragged=(256, 8192),
+                     name="qwen3-30b-a3b-shape bfp8, top-8 of 128, QK-norm, 128 sessions with contexts U{256..8192}, ragged bf16 KV"),
     "smollm": dict(model=dict(dim=576, heads=9, kv=3, layers=30, vocab=49152, ffn=1536, theta=10000.0, eps=1e-5, tied=True), mode="bfp8",
                    sequences=1, context=32, name="smollm-135m-shape bfp8, batch 1, 32-token prompt, bf16 KV"),
 }
@@ -88,20 +96,32 @@ class Clocks(threading.Thread):
                 "sm_max_mhz": float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)), "reasons": sorted(self.reasons)}
 
 
-def linear_bytes(c, sequences, fmt_bytes=1.0625):
-    """Algorithmic bytes of one step's block-float matmuls: packed weights once, activations in and out (bf16)."""
+def linear_bytes(c, sequences, fmt_bytes=1.0625, expert_bytes=None):
+    """Algorithmic bytes of one step's block-float matmuls: packed weights once, activations in and out (bf16).  A mixture
+    reads the experts some token picked: E (1 - (1 - k/E)^T) of them expected (the reference's cost model, ferrite/cost.py:91)."""
     hd = c.head_dim or c.dim // c.heads
-    shapes = [(c.dim, (c.heads + 2 * c.kv) * hd, (c.heads + 2 * c.kv) * hd), (c.heads * hd, c.dim, c.dim), (c.dim, 2 * c.ffn, c.ffn), (c.ffn, c.dim, c.dim)]
-    per_layer = sum(k * n * fmt_bytes + 2 * sequences * k + 2 * sequences * out for k, n, out in shapes)
+    shapes = [(c.dim, (c.heads + 2 * c.kv) * hd, (c.heads + 2 * c.kv) * hd, fmt_bytes), (c.heads * hd, c.dim, c.dim, fmt_bytes)]
+    launches = 2
+    if getattr(c, "experts", 0):
+        touched = c.experts * (1 - (1 - c.k / c.experts) ** max(sequences, 1))
+        eb = expert_bytes or fmt_bytes
+        shapes += [(c.dim, c.experts, c.experts, 2.0), (c.dim, touched * 2 * c.moe, touched * c.moe, eb), (touched * c.moe, c.dim, c.dim, eb)]
+        launches += 3
+    else:
+        shapes += [(c.dim, 2 * c.ffn, c.ffn, fmt_bytes), (c.ffn, c.dim, c.dim, fmt_bytes)]
+        launches += 2
+    per_layer = sum(k * n * b + 2 * sequences * k + 2 * sequences * out for k, n, out, b in shapes)
     head = c.dim * c.vocab_shard * fmt_bytes + 2 * sequences * c.dim + 4 * sequences * c.vocab_shard
-    return c.layers * per_layer + head, 4 * c.layers + 1
+    return c.layers * per_layer + head, launches * c.layers + 1
 
 
-def step_bytes(c, sequences, context):
-    """Algorithmic bytes a decode step reads per GPU: weights once, the KV rows each token sees, its embedding row."""
+def step_bytes(c, sequences, context_rows, expert_bytes=None):
+    """Algorithmic bytes a decode step reads per GPU: weights once, the KV rows each token sees (context_rows: their sum
+    over the sequences), its embedding row."""
     hd = c.head_dim or c.dim // c.heads
-    weights, _ = linear_bytes(c, 0)
-    kv = sequences * context * c.layers * 2 * c.kv * hd * 2
+    weights, _ = linear_bytes(c, sequences, expert_bytes=expert_bytes)
+    weights -= c.layers * 0  # (activations are part of linear_bytes; they are negligible)
+    kv = context_rows * c.layers * 2 * c.kv * hd * 2
     return weights + kv + sequences * c.dim * 2
 
 
@@ -128,6 +148,11 @@ def run_ferrite(args):
     S, ctx = wl["sequences"], wl["context"]
     part = ctx + args.steps + args.warmup + 64
     part += -part % 64
+    rng = np.random.default_rng(0)
+    # where each sequence stands: all at `context`, or (a serving mix) contexts drawn uniformly, seeded
+    ctxs = [int(v) for v in rng.integers(wl["ragged"][0], wl["ragged"][1] + 1, S)] if wl.get("ragged") else [ctx] * S
+    moe = bool(getattr(full, "experts", 0))
+    expert_bytes = 0.5625 if wl["mode"] == "experts" else None
     hd = llama.head(full)
     caches = []
     gen = torch.Generator(device=rt.device).manual_seed(1 + rank)
@@ -142,24 +167,24 @@ def run_ferrite(args):
 
     step = jit(step_fn)
     on = lambda row: Tensor.of(rt, [row], "int32")
-    rng = np.random.default_rng(0)
     ids0 = [int(v) for v in rng.integers(0, full.vocab, S)]
-    place = ctx
+    place = 0  # steps taken so far: sequence u stands at ctxs[u] + place
+    at = lambda: [v + place for v in ctxs]
     # the first two calls plan and record; they are part of the warm-up
     before = ops.KERNELS[0]
-    picks = step(on(ids0), on([place] * S))
+    picks = step(on(ids0), on(at()))
     place += 1
     per_step = None
     for i in range(max(args.warmup, 3) - 1):
         k0 = ops.KERNELS[0]
-        picks = step(on(picks.numpy().reshape(-1).tolist()), on([place] * S))
+        picks = step(on(picks.numpy().reshape(-1).tolist()), on(at()))
         if i == 0:
             per_step = ops.KERNELS[0] - k0  # kernels the recorded step holds (counted while it was recorded)
         place += 1
     rt.wait()
 
     # ---- device-resident loop: the pick feeds the next step on the device, places advance on the device
-    ids_t, places_t = on(picks.numpy().reshape(-1).tolist()), on([place] * S)
+    ids_t, places_t = on(picks.numpy().reshape(-1).tolist()), on(at())
     one = Tensor.of(rt, [[1] * S], "int32")
     bump = jit(lambda p: p + one)  # (records on its second call)
 
@@ -187,9 +212,9 @@ def run_ferrite(args):
 
     # ---- end to end: host ids and places in (pinned), picked tokens out, every step
     h_ids = torch.tensor([ids0], dtype=torch.int32).pin_memory()
-    h_places = torch.tensor([[place] * S], dtype=torch.int32).pin_memory()
+    h_places = torch.tensor([at()], dtype=torch.int32).pin_memory()
     h_out = torch.empty(1, 1, S, dtype=torch.int32).pin_memory()
-    d_ids, d_places = on(ids0), on([place] * S)
+    d_ids, d_places = on(ids0), on(at())
     e2e_steps = max(8, args.steps // 2)
     sync_all()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -207,33 +232,36 @@ def run_ferrite(args):
     ms_e2e = e2.elapsed_time(e3)
     clk = clocks.summary()
 
+    mm = None
+    lin_bytes, lin_launches = linear_bytes(c, S, expert_bytes=expert_bytes)
+    lin_ms = 0.0
     # ---- the dominant kernel alone: the step's block-float matmuls, back to back, every weight of the model once
-    x32 = Tensor.of(rt, rng.normal(0, 1, (S, full.dim)).astype(np.float32).tolist())
-    f32 = Tensor.of(rt, rng.normal(0, 1, (S, c.ffn)).astype(np.float32).tolist()) if c.ffn else None
-    a32 = Tensor.of(rt, rng.normal(0, 1, (S, c.heads * hd)).astype(np.float32).tolist())
+    # (a dense model; a mixture's indexed matmuls depend on the router's picks, so its roofline is the whole step's)
+    if not moe:
+        x32 = Tensor.of(rt, rng.normal(0, 1, (S, full.dim)).astype(np.float32).tolist())
+        f32 = Tensor.of(rt, rng.normal(0, 1, (S, c.ffn)).astype(np.float32).tolist())
+        a32 = Tensor.of(rt, rng.normal(0, 1, (S, c.heads * hd)).astype(np.float32).tolist())
 
-    def matmuls():
-        last = None
-        for p in w["_blocks"]:
-            last = x32.matmul(p["qkv_proj"]).realize()
-            last = a32.matmul(p["o_proj"]).realize()
-            last = x32.matmul(p["gate_up_proj"]).realize()
-            last = f32.matmul(p["down_proj"]).realize()
-        return x32.matmul(w["embed.T"], dtype="fp32").realize()
+        def matmuls():
+            for p in w["_blocks"]:
+                x32.matmul(p["qkv_proj"]).realize()
+                a32.matmul(p["o_proj"]).realize()
+                x32.matmul(p["gate_up_proj"]).realize()
+                f32.matmul(p["down_proj"]).realize()
+            return x32.matmul(w["embed.T"], dtype="fp32").realize()
 
-    mm = jit(lambda: matmuls())
-    for _ in range(3):
-        mm()
-    torch.cuda.synchronize()
-    e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 5
-    e4.record()
-    for _ in range(reps):
-        mm()
-    e5.record()
-    torch.cuda.synchronize()
-    lin_bytes, lin_launches = linear_bytes(c, S)
-    lin_ms = e4.elapsed_time(e5) / reps
+        mm = jit(lambda: matmuls())
+        for _ in range(3):
+            mm()
+        torch.cuda.synchronize()
+        e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        e4.record()
+        for _ in range(reps):
+            mm()
+        e5.record()
+        torch.cuda.synchronize()
+        lin_ms = e4.elapsed_time(e5) / reps
 
     # max over ranks
     times = torch.tensor([ms, ms_e2e, lin_ms], device=rt.device)
@@ -241,6 +269,10 @@ def run_ferrite(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, ms_e2e, lin_ms = times.tolist()
     peaks, peak_kind = measured_peaks()
+    rows_seen = sum(ctxs) + S * (args.warmup + args.steps // 2)  # KV rows the middle step of the timed run reads
+    whole = step_bytes(c, S, rows_seen, expert_bytes)
+    if moe:  # the roofline of a mixture's step as a whole: every kernel of it streams weights or KV rows
+        lin_bytes, lin_launches, lin_ms = whole, int(per_step or 1), ms / args.steps
     achieved = lin_bytes / (lin_ms * 1e-3) / 1e9
     line = {
         "metric": "decode tokens/s", "value": S * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -251,17 +283,17 @@ def run_ferrite(args):
         "e2e": {"value": S * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S, "d2h_bytes_per_step": 4 * S, "steps": e2e_steps},
         "gpu_launches": int(per_step or 0) * args.steps,
         "clocks": clk,
-        "roofline": {"bound": "hbm", "kernel": "linear_tcgen05_kernel (block-float dequant GEMM, %d tokens)" % S, "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": ("the whole decode step (indexed block-float matmuls + decode attention), %d tokens" if moe else
+                                                "linear_tcgen05_kernel (block-float dequant GEMM, %d tokens)") % S, "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_kind,
                      "traffic": 1.002 * lin_bytes / lin_launches, "traffic_source": "algorithmic bytes x 1.002 (DRAM read+write of the ncu capture in profiles/, 4096x14336 bfp8, 32 tokens)",
                      "launches": lin_launches, "us_per_launch": lin_ms * 1e3 / lin_launches, "bytes_per_launch": lin_bytes / lin_launches},
-        "step_roofline": {"algorithmic_bytes_per_gpu": step_bytes(c, S, ctx + args.warmup + args.steps // 2),
-                          "frac_of_hbm": step_bytes(c, S, ctx + args.warmup + args.steps // 2) / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+        "step_roofline": {"algorithmic_bytes_per_gpu": whole, "frac_of_hbm": whole / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }
     if rank == 0 and world == 1:
         del w, caches, step, mm
         torch.cuda.empty_cache()
-        if args.sweep:
+        if args.sweep and not moe:
             line["matmul_sweep"] = matmul_sweep(rt.device, peaks["hbm_gbs"])
         line["cpu_baseline"] = cpu_baseline(args, sample_seconds=20)
     if rank == 0:
@@ -344,25 +376,36 @@ def cpu_sample(args, seconds):
     c.layers = 1
     S, ctx = wl["sequences"], wl["context"]
     rng = np.random.default_rng(0)
+    ctxs = [int(v) for v in rng.integers(wl["ragged"][0], wl["ragged"][1] + 1, S)] if wl.get("ragged") else [ctx] * S
     hd, nh = ollama.head(c), c.heads + 2 * c.kv
-    q = lambda *shape: obuild.bfp_values(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02), wl["mode"])
+    fmt = "bfp8" if wl["mode"] == "experts" else wl["mode"]
+    q = lambda *shape, f=fmt: obuild.bfp_values(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02), f)
     w = {"layers.0.input_layernorm": np.ones((1, c.dim), np.float32), "layers.0.post_attention_layernorm": np.ones((1, c.dim), np.float32),
-         "layers.0.qkv_proj": q(c.dim, nh * hd), "layers.0.o_proj": q(c.heads * hd, c.dim), "layers.0.gate_up_proj": q(c.dim, 2 * c.ffn),
-         "layers.0.down_proj": q(c.ffn, c.dim), "norm": np.ones((1, c.dim), np.float32)}
+         "layers.0.qkv_proj": q(c.dim, nh * hd), "layers.0.o_proj": q(c.heads * hd, c.dim), "norm": np.ones((1, c.dim), np.float32)}
+    if getattr(c, "experts", 0):
+        ef = "bfp4" if wl["mode"] == "experts" else fmt
+        w["layers.0.router"] = (rng.standard_normal((c.dim, c.experts), dtype=np.float32) * np.float32(0.02))
+        w["layers.0.experts.gate_up"] = np.stack([q(c.dim, 2 * c.moe, f=ef) for _ in range(c.experts)])
+        w["layers.0.experts.down"] = np.stack([q(c.moe, c.dim, f=ef) for _ in range(c.experts)])
+        if wl["model"].get("qk_norm"):
+            w["layers.0.qk_norm"] = np.ones((nh, 1, hd), np.float32)
+            w["layers.0.qk_on"] = np.array([1.0] * (c.heads + c.kv) + [0.0] * c.kv, np.float32).reshape(nh, 1, 1)
+    else:
+        w["layers.0.gate_up_proj"], w["layers.0.down_proj"] = q(c.dim, 2 * c.ffn), q(c.ffn, c.dim)
     w["embed"] = (rng.standard_normal((c.vocab, c.dim), dtype=np.float32) * np.float32(0.02))
-    w["embed.T"] = obuild.bfp_values(np.ascontiguousarray(w["embed"].T), wl["mode"])
+    w["embed.T"] = obuild.bfp_values(np.ascontiguousarray(w["embed"].T), fmt)
     w["cos"], w["sin"] = ollama.rotary(c, c.places)
     part = ctx + 64
     caches = ollama.kv_cache(c, S * part)  # np.zeros: float64, as the reference's
     caches[0][:, :, :] = rng.standard_normal(caches[0].shape)
     ids = [int(v) for v in rng.integers(0, c.vocab, S)]
     slots = S if S > 1 else None
-    times, place = [], ctx
+    times, place = [], 0
     start = time.perf_counter()
     while not times or (time.perf_counter() - start < seconds and len(times) < 16):
         t0 = time.perf_counter()
         x = w["embed"][ids]
-        rows, cos, sin, mask, live = ollama.around(w, c, [place] * S if slots else [place], S * part if slots else part, slots)
+        rows, cos, sin, mask, live = ollama.around(w, c, [v + place for v in ctxs] if slots else [ctx + place], S * part if slots else part, slots)
         t_in = time.perf_counter()
         x = ollama.layer(x, ollama.block(w, "layers.0."), c, cos, sin, mask, caches[0], rows, live, slots)
         t_layer = time.perf_counter()

@@ -103,7 +103,8 @@ def linear_bytes(c, sequences, fmt_bytes=1.0625, expert_bytes=None):
     shapes = [(c.dim, (c.heads + 2 * c.kv) * hd, (c.heads + 2 * c.kv) * hd, fmt_bytes), (c.heads * hd, c.dim, c.dim, fmt_bytes)]
     launches = 2
     if getattr(c, "experts", 0):
-        touched = c.experts * (1 - (1 - c.k / c.experts) ** max(sequences, 1))
+        tp = getattr(c, "tp", None)  # expert parallel: a rank reads its share of the touched experts
+        touched = c.experts * (1 - (1 - c.k / c.experts) ** max(sequences, 1)) / (tp.world if tp else 1)
         eb = expert_bytes or fmt_bytes
         shapes += [(c.dim, c.experts, c.experts, 2.0), (c.dim, touched * 2 * c.moe, touched * c.moe, eb), (touched * c.moe, c.dim, c.dim, eb)]
         launches += 3
@@ -278,7 +279,7 @@ def run_ferrite(args):
         "metric": "decode tokens/s", "value": S * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}", "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
+        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}" + (f" (attention heads) + ep{world} (experts), all-reduce after o_proj and after the experts" if moe and world > 1 else ""), "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
                    "weights": "random N(0, 0.02) quantised on the device", "kv": "N(0, 1) bf16 standing in for the prompts' prefill"},
         "e2e": {"value": S * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S, "d2h_bytes_per_step": 4 * S, "steps": e2e_steps},
         "gpu_launches": int(per_step or 0) * args.steps,

@@ -102,13 +102,19 @@ def moe(h, p, c, live=None):
         w = values.softmax()
     else:
         w, ids = logits.softmax().topk(c.k)
-    return experts(h, p, ids, w if live is None else w * live)
+    return experts(h, p, ids, w if live is None else w * live, c)
 
 
-def experts(h, p, ids, w):
+def experts(h, p, ids, w, c=None):
+    """Expert parallel (c.tp): every rank routes every token (the router is replicated) and holds a run of the experts;
+    it runs the touched experts it holds - the others' entries index no expert and give zeros - so its result is a
+    partial sum, reduced over the ranks like a row-sharded down_proj's (`added`)."""
     gate_up, down = p["experts.gate_up"], p["experts.down"]
     m, e = down.rows, gate_up.batch
-    picks, weights = ids.touched(e, w.bfloat16().realize())
+    tp = getattr(c, "tp", None)
+    picks, weights = ids.touched(c.experts if tp else e, w.bfloat16().realize())
+    if tp:
+        picks = (picks - tp.rank * e).realize()  # global expert -> its place among this rank's, or out of range
     x = h.matmul(gate_up, index=picks)
     g = glu(x[:, :, :m], x[:, :, m:])
     return (g * weights).matmul(down, index=picks).sum(0)
@@ -140,6 +146,7 @@ def tensor_parallel(c, rank, world, group=None):
     """c as rank `rank` of `world` holds it: its share of the query and key heads, of the MLP's columns and of the
     vocabulary (models too large or too slow for one GPU; the reference has no counterpart: one chip, ferrite/runtime.py:304-311)."""
     assert c.heads % world == 0 and c.kv % world == 0 and (c.ffn or 0) % world == 0 and c.vocab % (16 * world) == 0, "shards of whole heads and runs"
+    assert (getattr(c, "experts", 0) or 0) % world == 0, "every rank holds the same number of whole experts"
     local = SimpleNamespace(**vars(c))
     local.head_dim, local.heads, local.kv, local.dim = head(c), c.heads // world, c.kv // world, c.dim
     local.ffn, local.vocab_shard = (c.ffn or 0) // world, c.vocab // world
@@ -150,7 +157,8 @@ def tensor_parallel(c, rank, world, group=None):
 def tp_keep(name, full, rank, world):
     """What rank `rank` of `world` keeps of the weight called `name`: (axis, indices) into the whole matrix, or None for
     a weight every rank holds whole.  qkv_proj: its heads' columns of q, of k and of v; gate_up_proj: its columns of the
-    gate half and of the up half; o_proj and down_proj: the matching rows; embed.T: its run of the vocabulary."""
+    gate half and of the up half; o_proj and down_proj: the matching rows; embed.T: its run of the vocabulary; a
+    mixture's experts: its run of whole experts (the router stays whole on every rank)."""
     hd, H, KV = head(full), full.heads, full.kv
     run = lambda first, size: np.arange(first + rank * (size // world), first + (rank + 1) * (size // world))
     op = name.split(".")[-1]
@@ -164,6 +172,8 @@ def tp_keep(name, full, rank, world):
         return 0, run(0, full.ffn)
     if name == "embed.T":
         return 1, run(0, full.vocab)
+    if name.endswith(("experts.gate_up", "experts.down")):
+        return 0, run(0, full.experts)
     return None
 
 
@@ -318,8 +328,8 @@ def random_weights(rt, c, prec=None, seed=0, scale=0.02, full=None):
             w[pre + "qk_norm"] = Tensor.of(rt, np.ones((c.heads + c.kv, 1, hd), np.float32))
         if full.experts:
             w[pre + "router"] = keep(pre + "router", draw(d, full.experts))
-            w[pre + "experts.gate_up"] = keep(pre + "experts.gate_up", draw(full.experts, d, 2 * full.moe))
-            w[pre + "experts.down"] = keep(pre + "experts.down", draw(full.experts, full.moe, d))
+            w[pre + "experts.gate_up"] = keep(pre + "experts.gate_up", draw(full.experts, d, 2 * full.moe), mine(pre + "experts.gate_up"))
+            w[pre + "experts.down"] = keep(pre + "experts.down", draw(full.experts, full.moe, d), mine(pre + "experts.down"))
         else:
             w[pre + "gate_up_proj"] = keep(pre + "gate_up_proj", draw(d, 2 * full.ffn), mine(pre + "gate_up_proj"))
             w[pre + "down_proj"] = keep(pre + "down_proj", draw(full.ffn, d), mine(pre + "down_proj"))

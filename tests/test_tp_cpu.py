@@ -54,6 +54,56 @@ def _worker(rank, world, port, result):
     dist.destroy_process_group()
 
 
+def _expert_worker(rank, world, port, result):
+    """Expert parallelism as ferrite_b200.llama.experts does it: every rank routes every token, keeps a run of whole
+    experts (tp_keep), maps the touched experts' global ids to its own places (out of range: no expert, zeros) and
+    computes a partial sum; the all-reduce gives the one-device mixture (oracle.llama.experts)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from ferrite_b200 import llama
+    E, k, d, F, T = 8, 2, 32, 48, 6
+    full = llama.model(dim=d, heads=4, kv=2, layers=1, vocab=256, ffn=0, experts=E, k=k, moe=F, eps=1e-5, theta=10000.0)
+    rng = np.random.default_rng(3)
+    gate_up, down = rng.normal(0, 0.2, (E, d, 2 * F)), rng.normal(0, 0.2, (E, F, d))
+    h = rng.normal(0, 1, (T, d))
+    logits = h @ rng.normal(0, 0.5, (d, E))
+    values, ids = ollama.topk(logits, k)
+    wts = ollama.softmax(values)
+    want = ollama.experts(h, {"experts.gate_up": gate_up, "experts.down": down}, ids, wts)
+    axis, kept = llama.tp_keep("layers.0.experts.gate_up", full, rank, world)
+    assert axis == 0 and llama.tp_keep("layers.0.experts.down", full, rank, world)[1].tolist() == kept.tolist()
+    assert llama.tp_keep("layers.0.router", full, rank, world) is None
+    mine_gu, mine_down = gate_up[kept], down[kept]
+    picks, weights = ollama.touched(ids, wts, E)  # global ids ascending, then E (none); weights [slots, T, 1]
+    local = np.asarray(picks).reshape(-1) - rank * len(kept)
+    partial = np.zeros((T, d))
+    for slot, e in enumerate(local):
+        if 0 <= e < len(kept):
+            x = h @ mine_gu[e]
+            partial += (ollama.glu(x[:, :F], x[:, F:]) * np.asarray(weights)[slot].reshape(T, 1)) @ mine_down[e]
+    total = torch.from_numpy(partial.copy())
+    dist.all_reduce(total)
+    ok = np.allclose(total.numpy(), np.asarray(want, dtype=np.float64).reshape(T, d), rtol=1e-9, atol=1e-9)
+    every = [torch.zeros(len(kept), dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(every, torch.from_numpy(np.asarray(kept, dtype=np.int64)))
+    ok &= sorted(torch.cat(every).tolist()) == list(range(E))
+    if rank == 0:
+        result.put(bool(ok))
+    dist.destroy_process_group()
+
+
+def test_two_ranks_of_experts_reproduce_the_mixture():
+    ctx = mp.get_context("spawn")
+    result, port = ctx.Queue(), _free_port()
+    procs = [ctx.Process(target=_expert_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert result.get(timeout=5) is True
+
+
 def test_two_ranks_reproduce_one_device():
     ctx = mp.get_context("spawn")
     result, port = ctx.Queue(), _free_port()

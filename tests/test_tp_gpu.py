@@ -1,5 +1,6 @@
 """Tensor parallelism on two GPUs: the ranks' sharded decoder (NCCL all-reduce after o_proj and down_proj, sharded
-vocabulary pick) must give the single-GPU decoder's tokens and logits.  Skipped on a box with one GPU."""
+vocabulary pick) must give the single-GPU decoder's tokens and logits - for a dense decoder and for a mixture whose
+experts are spread over the ranks (all-reduce after the experts).  Skipped on a box with one GPU."""
 import os
 import socket
 
@@ -10,15 +11,22 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, result):
+MODELS = {
+    "dense": (dict(dim=512, heads=8, kv=4, layers=2, vocab=1024, ffn=1024, eps=1e-5, theta=10000.0, places=64), "bfp8"),
+    "mixture": (dict(dim=512, heads=8, kv=4, layers=2, vocab=1024, ffn=0, experts=8, k=2, moe=256, norm_topk=True, eps=1e-5, theta=10000.0, places=64),
+                "experts"),
+}
+
+
+def _worker(rank, world, port, result, kind="dense"):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     from ferrite_b200 import llama
     from ferrite_b200.tensor import Runtime, Tensor, jit
     rt = Runtime(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=rt.device)
-    full = llama.model(dim=512, heads=8, kv=4, layers=2, vocab=1024, ffn=1024, eps=1e-5, theta=10000.0, places=64)
-    prec = llama.precision(full, "bfp8")
+    full = llama.model(**MODELS[kind][0])
+    prec = llama.precision(full, MODELS[kind][1])
     c = llama.tensor_parallel(full, rank, world, dist.group.WORLD)
     w = llama.random_weights(rt, c, prec, seed=5, full=full, scale=0.05)
     S, part = 4, 32
@@ -50,7 +58,8 @@ def _worker(rank, world, port, result):
     os._exit(0)  # (no NCCL teardown: the recorded graphs still hold its kernels)
 
 
-def test_two_gpus_decode_like_one(cuda):
+@pytest.mark.parametrize("kind", ["dense", "mixture"])
+def test_two_gpus_decode_like_one(cuda, kind):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -59,7 +68,7 @@ def test_two_gpus_decode_like_one(cuda):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, result)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, result, kind)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

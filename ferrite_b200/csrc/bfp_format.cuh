@@ -75,6 +75,32 @@ __device__ __forceinline__ void unpack4_word(uint32_t w, uint32_t s2, uint32_t o
   }
 }
 
+// The masked words alone (no multiplies): each half of a register is a column's sign and magnitude standing where a
+// bf16 subnormal's are, i.e. half << 16 read as an fp32 is the (fp32-denormal) number +-mag * 2^-133 (bfp4: its 3-bit
+// magnitude m, for a value of +-16m * 2^(top-133)).  A consumer that multiplies by an fp32 anyway folds 2^top into that
+// factor and needs no unpack arithmetic at all.  Eight registers per run: columns 2i, 2i+1 in register i.
+template <int FMT>
+__device__ __forceinline__ void mask_run(const uint32_t* words, uint32_t m[8]) {
+  if (FMT == FB_BFP8) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      uint32_t r;
+      asm("lop3.b32 %0, %1, 0x807F807F, 0, 0xC0;" : "=r"(m[2 * h]) : "r"(words[h]));
+      asm("shf.r.wrap.b32 %0, %1, %1, 8;" : "=r"(r) : "r"(words[h]));
+      asm("lop3.b32 %0, %1, 0x807F807F, 0, 0xC0;" : "=r"(m[2 * h + 1]) : "r"(r));
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t r = words[h];
+        if (i) asm("shf.r.wrap.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(words[h]), "r"(4 * i));
+        asm("lop3.b32 %0, %1, 0x80078007, 0, 0xC0;" : "=r"(m[4 * h + i]) : "r"(r));
+      }
+  }
+}
+
 // A whole run of 16 columns as eight bf16-pair registers (columns 2i, 2i+1 in register i).
 __device__ __forceinline__ void unpack_run8(uint4 raw, uint32_t top, uint32_t v[8]) {
   const uint32_t s2 = scale8(top);

@@ -9,7 +9,6 @@ namespace fb {
 // take the gate's block, 4-7 the up's).  See gemv.cuh for the per-lane work.
 template <int FMT, int M, bool NORM>
 __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
-  griddep_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool swiglu = a.epilogue == FB_EPI_SWIGLU;
   const int G = swiglu ? 4 : 8;
@@ -34,6 +33,9 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
   }
   gemv_accumulate<FMT, M, NORM>(col, (int)(b % GROUP_RUNS), static_cast<const uint16_t*>(a.x), a.ldx, static_cast<const uint16_t*>(a.norm_w), K,
                                 wg * 128, G * 128, acc, ss);
+  // Only now may the next kernel's CTAs move in beside this one's (four of these fit an SM): were they let in at the
+  // start, the L2 prefetches of several kernels ahead would compete with this kernel's loads and evict one another.
+  griddep_launch_dependents();
 
   __shared__ float red[8][M][16];
   __shared__ float ssred[8][M];
@@ -55,6 +57,7 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
     if (w < G) v += red[w][t][j]; else u += red[w][t][j];
     if (NORM && w < G) s2 += ssred[w][t];  // a group's lanes read every row once
   }
+  v *= GEMV_ACC_SCALE, u *= GEMV_ACC_SCALE;
   if (NORM) {
     float rstd = rsqrtf(s2 / (float)K + a.eps);
     v *= rstd, u *= rstd;
@@ -70,8 +73,15 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
 template <int FMT, int M>
 static void launch_gemv(const LinearArgs& a, cudaStream_t s) {
   unsigned blocks = (unsigned)(a.N / 16 / (a.epilogue == FB_EPI_SWIGLU ? 2 : 1));
-  if (a.norm_w) linear_gemv_kernel<FMT, M, true><<<blocks, 256, 0, s>>>(a);
-  else linear_gemv_kernel<FMT, M, false><<<blocks, 256, 0, s>>>(a);
+  // a programmatic dependent of the kernel before it: the L2 prefetch and the first weight loads do not wait for it
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(256), cfg.dynamicSmemBytes = 0, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  if (a.norm_w) cudaLaunchKernelEx(&cfg, linear_gemv_kernel<FMT, M, true>, a);
+  else cudaLaunchKernelEx(&cfg, linear_gemv_kernel<FMT, M, false>, a);
 }
 
 template <int FMT>

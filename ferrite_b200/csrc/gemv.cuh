@@ -10,6 +10,8 @@
 
 namespace fb {
 
+constexpr float GEMV_ACC_SCALE = 18446744073709551616.f;  // 2^64: gemv_accumulate's sums are kept scaled by 2^-64
+
 template <int FMT>
 struct RunBytes { static constexpr int value = FMT == FB_BFP8 ? 16 : 8; };
 
@@ -53,6 +55,7 @@ __device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ col,
   int64_t k0 = k_first + 4 * lane;
   Raw4<FMT> cur, nxt;
   if (k0 < K) load_raw4<FMT>(cur, col, run, k0);
+  griddep_wait();  // the weights above are nobody's output; the activations below are the kernel before's
   for (; k0 < K; k0 += k_step) {
     int64_t kn = k0 + k_step;
     if (kn < K) load_raw4<FMT>(nxt, col, run, kn);
@@ -76,17 +79,35 @@ __device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ col,
         }
       }
     }
+    // The sums are kept scaled by 2^-64 (GEMV_ACC_SCALE undoes it): the weight enters the FMA as the fp32 denormal
+    // +-mag * 2^-133 its masked bits already are, and 2^(top-64) goes into the activation - one multiply per run and
+    // token instead of unpack arithmetic per value.  The products are exact inside the FMA either way, so the sums
+    // round as those of the unpacked values do.  (Shared exponents above 186 - values beyond 2^53 - would overflow
+    // that factor: such a run takes the unpacked route, its activations scaled by 2^-64.)
+    constexpr uint32_t LIFT = FMT == FB_BFP8 ? 63 : 67;  // bfp4's 3-bit magnitude stands for 16 times itself
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t top = (cur.tops >> (8 * kk)) & 255u;
       uint32_t v[8];
-      unpack_row<FMT>(cur, kk, v);
+      float xs[M];
+      if (top <= 186) {
+        const uint32_t* words = reinterpret_cast<const uint32_t*>(cur.q) + kk * (FMT == FB_BFP8 ? 4 : 2);
+        mask_run<FMT>(words, v);
+        const float lift = __uint_as_float((top + LIFT) << 23);
+#pragma unroll
+        for (int t = 0; t < M; ++t) xs[t] = xv[t][kk] * lift;
+      } else {
+        unpack_row<FMT>(cur, kk, v);
+#pragma unroll
+        for (int t = 0; t < M; ++t) xs[t] = xv[t][kk] * 5.421010862427522e-20f;  // 2^-64
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float lo = __uint_as_float(v[i] << 16), hi = __uint_as_float(v[i] & 0xFFFF0000u);
 #pragma unroll
         for (int t = 0; t < M; ++t) {
-          acc[t][2 * i] = fmaf(lo, xv[t][kk], acc[t][2 * i]);
-          acc[t][2 * i + 1] = fmaf(hi, xv[t][kk], acc[t][2 * i + 1]);
+          acc[t][2 * i] = fmaf(lo, xs[t], acc[t][2 * i]);
+          acc[t][2 * i + 1] = fmaf(hi, xs[t], acc[t][2 * i + 1]);
         }
       }
     }

@@ -54,6 +54,7 @@ def parse():
     ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="fewer blocks than the model has (a smoke run; the JSON line says so)")
     ap.add_argument("--impl", default="ferrite_b200", choices=["ferrite_b200", "reference"])
+    ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"], help="several GPUs: how the ranks' partial sums are added")
     ap.add_argument("--sweep", type=int, default=1, help="0: leave the isolated matmul sweep out of the line (a profiling run)")
     ap.add_argument("--matmul", default="", help="M,K,N,fmt[,calls]: only that isolated matmul (RMSNorm + SwiGLU fused), e.g. 32,4096,14336,bfp8,6")
     return ap.parse_args()
@@ -144,6 +145,15 @@ def run_ferrite(args):
     c = llama.tensor_parallel(full, rank, world, dist.group.WORLD) if world > 1 else full
     if world == 1:
         c.vocab_shard = full.vocab
+    reduction = "none"
+    if world > 1:
+        reduction = "nccl all-reduce + add"
+        if args.reduce == "peer":
+            try:  # this library's kernel over NVLink peer memory; NCCL's all-reduce if the mapping cannot be set up here
+                llama.peer_reduce(rt, c, wl["sequences"])
+                reduction = "fb_peer_reduce_add (own kernel, peer loads over NVLink, residual fused)"
+            except Exception as e:  # noqa: BLE001
+                reduction += f" (peer memory unavailable: {type(e).__name__})"
     prec = llama.precision(full, wl["mode"])
     w = llama.random_weights(rt, c, prec, seed=0, full=full)
     S, ctx = wl["sequences"], wl["context"]
@@ -232,6 +242,8 @@ def run_ferrite(args):
     sync_all()
     ms_e2e = e2.elapsed_time(e3)
     clk = clocks.summary()
+    if getattr(getattr(c, "tp", None), "peer", None) is not None:
+        c.tp.peer.check()
 
     mm = None
     lin_bytes, lin_launches = linear_bytes(c, S, expert_bytes=expert_bytes)
@@ -279,7 +291,7 @@ def run_ferrite(args):
         "metric": "decode tokens/s", "value": S * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}" + (f" (attention heads) + ep{world} (experts), all-reduce after o_proj and after the experts" if moe and world > 1 else ""), "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
+        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}" + (f" (attention heads) + ep{world} (experts), all-reduce after o_proj and after the experts" if moe and world > 1 else ""), "reduction": reduction, "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
                    "weights": "random N(0, 0.02) quantised on the device", "kv": "N(0, 1) bf16 standing in for the prompts' prefill"},
         "e2e": {"value": S * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S, "d2h_bytes_per_step": 4 * S, "steps": e2e_steps},
         "gpu_launches": int(per_step or 0) * args.steps,

@@ -134,6 +134,17 @@ def added(x, y, c):
     tp = getattr(c, "tp", None)
     if not tp:
         return x + y
+    peer = getattr(tp, "peer", None)
+    if peer is not None and x.batch == 1 and x.dtype == "bf16":
+        # this library's kernel over NVLink peer memory: the partial is computed straight into memory every rank maps,
+        # then one kernel per rank adds all the partials and the residual (ferrite_b200/peer.py)
+        xr = x.realize()
+        xr = xr if xr.buf.is_contiguous() else (xr + 0).realize()
+        stage = Tensor(x.rt, x.rows, x.cols, buf=peer.stage(x.rows, x.cols))
+        y.realize(into=stage)
+        out = Tensor(x.rt, x.rows, x.cols)
+        peer.reduce_add(x.rows * x.cols, xr.buf, out.buf)
+        return out
     import torch.distributed as dist
     out = (x + y if tp.rank == 0 else y).realize()
     if not out.buf.is_contiguous() or out.owner is not None:
@@ -150,8 +161,16 @@ def tensor_parallel(c, rank, world, group=None):
     local = SimpleNamespace(**vars(c))
     local.head_dim, local.heads, local.kv, local.dim = head(c), c.heads // world, c.kv // world, c.dim
     local.ffn, local.vocab_shard = (c.ffn or 0) // world, c.vocab // world
-    local.tp = SimpleNamespace(rank=rank, world=world, group=group)
+    local.tp = SimpleNamespace(rank=rank, world=world, group=group, peer=None)
     return local
+
+
+def peer_reduce(rt, c, tokens):
+    """Give c (from tensor_parallel) this library's NVLink reduction for its blocks' partial sums instead of NCCL's
+    all-reduce: 2 sites a block, each `tokens` rows of the model's width.  Collective over c.tp.group."""
+    from .peer import PeerReduce
+    c.tp.peer = PeerReduce(rt, c.tp.group, tokens * c.dim, 2 * c.layers)
+    return c
 
 
 def tp_keep(name, full, rank, world):
@@ -228,6 +247,8 @@ def forward(ids, places, w, c, caches, slots=None, every=False, length=None):
     tensors; caches each block's keys' heads then its values'; slots: several sequences decoding together, their caches
     side by side, the logits every token's."""
     x = w["embed"].gather(ids)
+    if getattr(getattr(c, "tp", None), "peer", None) is not None:
+        c.tp.peer.new_step()
     size = caches[0].rows
     rows, seen, live = around(w, c, places, size, slots, length)
     rotary = (w["cos"], w["sin"], places)

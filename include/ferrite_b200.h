@@ -224,6 +224,21 @@ int fb_reduce(int is_max, const void* in, const int64_t* in_strides_host, int in
 int fb_matmul(const void* a, const int64_t* a_strides_host, int a_dtype, const void* b, const int64_t* b_strides_host, int b_dtype,
               void* c, const int64_t* c_strides_host, int c_dtype, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* ---- several GPUs -------------------------------------------------------------------------------------- */
+
+/* out = residual + sum over the ranks of their partials, bf16 [count], one kernel per rank reading the other ranks'
+ * partials out of their memory over NVLink (plain peer loads).  No counterpart in the reference, which drives one chip
+ * (ferrite/runtime.py:304-311); it stands where a tensor-parallel block all-reduces o_proj's / down_proj's / the
+ * experts' partial sums and adds the residual (models/llama.py:95-109).
+ * partials[r], flags[r]: HOST arrays of `world` device addresses, valid on this GPU, of rank r's partial for this call
+ * site and of rank r's flag words (`world` uint32, zero before the first call); every rank passes the same buffers in
+ * the same order and makes the same sequence of calls.  state: 4 uint32 of this GPU, zero before the first call
+ * ([0] counts the calls; [2] holds 201 + r after a bounded wait for rank r gave up, else 0).  The partial of a call
+ * site may be overwritten as soon as a later call has been launched behind this one.  count: a multiple of 8.
+ * All ranks add in rank order, so their results are bit-identical. */
+int fb_peer_reduce_add(const void* const* partials, void* const* flags, int rank, int world, void* state, int64_t count,
+                       const void* residual, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,7 +18,7 @@ MODELS = {
 }
 
 
-def _worker(rank, world, port, result, kind="dense"):
+def _worker(rank, world, port, result, kind="dense", peer=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     from ferrite_b200 import llama
@@ -28,6 +28,8 @@ def _worker(rank, world, port, result, kind="dense"):
     full = llama.model(**MODELS[kind][0])
     prec = llama.precision(full, MODELS[kind][1])
     c = llama.tensor_parallel(full, rank, world, dist.group.WORLD)
+    if peer:  # this library's reduction over NVLink peer memory instead of NCCL's all-reduce
+        llama.peer_reduce(rt, c, 4)
     w = llama.random_weights(rt, c, prec, seed=5, full=full, scale=0.05)
     S, part = 4, 32
     on = lambda row: Tensor.of(rt, [row], "int32")
@@ -53,13 +55,15 @@ def _worker(rank, world, port, result, kind="dense"):
         result.put((agree, worst))
         import time
         time.sleep(1)  # let the queue's feeder thread send before the hard exit
+    if peer:
+        c.tp.peer.check()
     dist.barrier()
     torch.cuda.synchronize()
     os._exit(0)  # (no NCCL teardown: the recorded graphs still hold its kernels)
 
 
-@pytest.mark.parametrize("kind", ["dense", "mixture"])
-def test_two_gpus_decode_like_one(cuda, kind):
+@pytest.mark.parametrize("kind,peer", [("dense", False), ("mixture", False), ("dense", True), ("mixture", True)])
+def test_two_gpus_decode_like_one(cuda, kind, peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -68,7 +72,7 @@ def test_two_gpus_decode_like_one(cuda, kind):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, result, kind)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, result, kind, peer)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

@@ -149,11 +149,18 @@ def run_ferrite(args):
     if world > 1:
         reduction = "nccl all-reduce + add"
         if args.reduce == "peer":
+            why = ""
             try:  # this library's kernel over NVLink peer memory; NCCL's all-reduce if the mapping cannot be set up here
                 llama.peer_reduce(rt, c, wl["sequences"])
-                reduction = "fb_peer_reduce_add (own kernel, peer loads over NVLink, residual fused)"
             except Exception as e:  # noqa: BLE001
-                reduction += f" (peer memory unavailable: {type(e).__name__})"
+                why = type(e).__name__
+            ok = torch.tensor([0 if why else 1], device=rt.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # every rank takes the same path
+            if int(ok.item()):
+                reduction = "fb_peer_reduce_add (own kernel, peer loads over NVLink, residual fused)"
+            else:
+                c.tp.peer = None
+                reduction += f" (peer memory unavailable on some rank{': ' + why if why else ''})"
     prec = llama.precision(full, wl["mode"])
     w = llama.random_weights(rt, c, prec, seed=0, full=full)
     S, ctx = wl["sequences"], wl["context"]

@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(256) peer_reduce_add_kernel(const PeerArgs a) 
     __threadfence_system();
     store_release_sys(a.flags[threadIdx.x] + a.rank, e);
   }
-  if (threadIdx.x < a.world) {  // one thread per rank waited for
+  // (after a wait has given up once, later calls do not wait again: the caller finds the code in state[2] within seconds)
+  if (threadIdx.x < a.world && *reinterpret_cast<volatile uint32_t*>(a.state + 2) == 0) {  // one thread per rank waited for
     const uint32_t* flag = a.flags[a.rank] + threadIdx.x;
     const long long start = clock64();
     // (flags only grow; the difference is taken modulo 2^32 so that the count may wrap)

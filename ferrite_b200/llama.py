@@ -169,7 +169,9 @@ def peer_reduce(rt, c, tokens):
     """Give c (from tensor_parallel) this library's NVLink reduction for its blocks' partial sums instead of NCCL's
     all-reduce: 2 sites a block, each `tokens` rows of the model's width.  Collective over c.tp.group."""
     from .peer import PeerReduce
-    c.tp.peer = PeerReduce(rt, c.tp.group, tokens * c.dim, 2 * c.layers)
+    peer = PeerReduce(rt, c.tp.group, tokens * c.dim, 2 * c.layers)
+    peer.selftest()
+    c.tp.peer = peer
     return c
 
 

@@ -49,6 +49,20 @@ class PeerReduce:
         ops.count()
         self.next_site += 1
 
+    def selftest(self):
+        """Three small reductions of known values; raises if a rank does not arrive or a sum is wrong.  Collective."""
+        n = min(self.count, 4096)
+        out = torch.empty(n, dtype=torch.bfloat16, device=self.rt.device)
+        for i in range(3):
+            self.new_step()
+            self.stage(1, n).fill_(float(self.rank + 1 + i))
+            self.reduce_add(n, None, out)
+            torch.cuda.synchronize(self.rt.device)
+            self.check()
+            want = float(sum(r + 1 + i for r in range(self.world)))
+            assert bool((out.float() == want).all()), f"fb_peer_reduce_add gave {out[:4].tolist()} for {want}"
+        self.new_step()
+
     def new_step(self):
         self.next_site = 0
 

@@ -37,7 +37,7 @@ SIGNATURES = {
     "fb_attend_workspace_bytes": (_sz, [_i64, _i64, _i, _i64]),
     "fb_attend": (_i, [_p, _i64, _i64, _i, _i64, _i64, _p, _p, _i64, _i64, _i64, _p, _i64, _i64, _i, _f, _p, _p, _sz, _p]),
     "fb_topk": (_i, [_i, _p, _i64, _i64, _i64, _i, _p, _p, _p, _p, _i64, _p]),
-    "fb_touched": (_i, [_p, _p, _i64, _i, _i, _p, _p, _p]),
+    "fb_touched": (_i, [_p, _p, _i64, _i, _i, _i, _p, _p, _p]),
     "fb_elementwise": (_i, [_i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _p]),
     "fb_reduce": (_i, [_i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _i, _p]),
     "fb_matmul": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),

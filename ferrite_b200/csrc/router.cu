@@ -63,15 +63,16 @@ __global__ void __launch_bounds__(256) topk_kernel(const T* __restrict__ x, int6
 }
 
 // One block: experts some row picks with a weight that is not zero, ascending, then n; and each entry's weight per row.
+// Experts are counted from `first`: a rank that holds experts first .. first + n - 1 lists those, numbered from 0.
 __global__ void __launch_bounds__(256) touched_kernel(const int32_t* __restrict__ ids, const uint16_t* __restrict__ w, int64_t rows, int k, int n,
-                                                      int slots, int32_t* __restrict__ experts, uint16_t* __restrict__ out) {
+                                                      int first, int slots, int32_t* __restrict__ experts, uint16_t* __restrict__ out) {
   griddep_launch_dependents();
   extern __shared__ int32_t flag[];  // [n] then the compacted list [slots]
   int32_t* listed = flag + n;
   for (int e = threadIdx.x; e < n; e += blockDim.x) flag[e] = 0;
   __syncthreads();
   for (int64_t i = threadIdx.x; i < rows * k; i += blockDim.x) {
-    const int32_t e = ids[i];
+    const int32_t e = ids[i] - first;
     if (e >= 0 && e < n && (w[i] & 0x7FFFu) != 0) flag[e] = 1;  // (+0 and -0 are both zero)
   }
   __syncthreads();
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(256) touched_kernel(const int32_t* __restrict_
     float acc = 0.f;
     bool any = false;
     for (int j = 0; j < k; ++j)
-      if (e < n && ids[r * k + j] == e) acc += bf16_bits_to_float(w[r * k + j]), any = true;
+      if (e < n && ids[r * k + j] - first == e) acc += bf16_bits_to_float(w[r * k + j]), any = true;
     out[i] = any ? (uint16_t)float_to_bf16_bits(acc) : 0;
   }
 }
@@ -109,10 +110,11 @@ extern "C" int fb_topk(int dtype, const void* x, int64_t rows, int64_t cols, int
   return fb::launch_status("fb_topk");
 }
 
-extern "C" int fb_touched(const int32_t* ids, const void* weights_bf16, int64_t rows, int k, int n, int32_t* experts, void* out_bf16, void* stream) {
+extern "C" int fb_touched(const int32_t* ids, const void* weights_bf16, int64_t rows, int k, int n, int first, int32_t* experts, void* out_bf16,
+                          void* stream) {
   FB_REQUIRE(ids && weights_bf16 && experts && out_bf16 && rows >= 1 && k >= 1 && k <= 32 && n >= 1 && n <= 4096, "fb_touched: up to 32 choices of up to 4096 experts");
   const int slots = (int)(rows * k < n ? rows * k : n);
-  fb::touched_kernel<<<1, 256, (size_t)(n + slots) * sizeof(int32_t), (cudaStream_t)stream>>>(ids, (const uint16_t*)weights_bf16, rows, k, n, slots, experts,
+  fb::touched_kernel<<<1, 256, (size_t)(n + slots) * sizeof(int32_t), (cudaStream_t)stream>>>(ids, (const uint16_t*)weights_bf16, rows, k, n, first, slots, experts,
                                                                                            (uint16_t*)out_bf16);
   return fb::launch_status("fb_touched");
 }

@@ -107,14 +107,12 @@ def moe(h, p, c, live=None):
 
 def experts(h, p, ids, w, c=None):
     """Expert parallel (c.tp): every rank routes every token (the router is replicated) and holds a run of the experts;
-    it runs the touched experts it holds - the others' entries index no expert and give zeros - so its result is a
-    partial sum, reduced over the ranks like a row-sharded down_proj's (`added`)."""
+    it lists and runs the touched experts it holds, so its result is a partial sum, reduced over the ranks like a
+    row-sharded down_proj's (`added`)."""
     gate_up, down = p["experts.gate_up"], p["experts.down"]
     m, e = down.rows, gate_up.batch
     tp = getattr(c, "tp", None)
-    picks, weights = ids.touched(c.experts if tp else e, w.bfloat16().realize())
-    if tp:
-        picks = (picks - tp.rank * e).realize()  # global expert -> its place among this rank's, or out of range
+    picks, weights = ids.touched(e, w.bfloat16().realize(), first=tp.rank * e if tp else 0)
     x = h.matmul(gate_up, index=picks)
     g = glu(x[:, :, :m], x[:, :, m:])
     return (g * weights).matmul(down, index=picks).sum(0)

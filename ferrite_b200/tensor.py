@@ -458,16 +458,17 @@ class Tensor:
         self.rt.launched("topk", parts)
         return values, ids
 
-    def touched(self, n, weights):
+    def touched(self, n, weights, first=0):
         """The experts some row picks by a weight that is not 0, each once, ascending, then n (none); and each entry's
-        weight from each row (ferrite/tensor.py:403-416)."""
+        weight from each row (ferrite/tensor.py:403-416).  first: count the experts from it (a rank's run of a mixture's
+        experts: only those are listed, numbered from 0)."""
         assert self.dtype == "int32" and weights.dtype == "bf16" and self.shape == weights.shape and self.batch == 1 and self.cols <= 32
         x, w = self.realize(), weights.realize()
         x = x if x.buf.is_contiguous() else (x + 0).realize()
         w = w if w.buf.is_contiguous() else (w + 0).realize()
         slots = min(self.rows * self.cols, n)
         experts, out = Tensor(self.rt, slots, 1, dtype="int32"), Tensor(self.rt, self.rows, 1, batch=slots)
-        check(lib().fb_touched(x.buf.data_ptr(), w.buf.data_ptr(), self.rows, self.cols, n, experts.buf.data_ptr(), out.buf.data_ptr(), ops._stream()))
+        check(lib().fb_touched(x.buf.data_ptr(), w.buf.data_ptr(), self.rows, self.cols, n, first, experts.buf.data_ptr(), out.buf.data_ptr(), ops._stream()))
         self.rt.launched("touched", 1)
         return experts, out
 

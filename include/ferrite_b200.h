@@ -200,8 +200,11 @@ int fb_topk(int dtype, const void* x, int64_t rows, int64_t cols, int64_t ldx, i
 
 /* Tensor.touched (ferrite/tensor.py:403-416, ferrite/compiler.py:1898-1905): from ids and bf16 weights [rows, k]
  * (experts below n), experts[min(rows*k, n)]: those some row picks by a weight that is not 0, ascending, then n
- * ("none"); out_bf16[entry, row]: the row's weight for that entry's expert, 0 where it did not pick it. */
-int fb_touched(const int32_t* ids, const void* weights_bf16, int64_t rows, int k, int n, int32_t* experts, void* out_bf16, void* stream);
+ * ("none"); out_bf16[entry, row]: the row's weight for that entry's expert, 0 where it did not pick it.
+ * first (0 for the reference's behaviour): experts are counted from it - a rank holding experts first .. first+n-1 of
+ * a mixture spread over several GPUs lists only those, numbered from 0, and ignores the picks of other ranks' experts. */
+int fb_touched(const int32_t* ids, const void* weights_bf16, int64_t rows, int k, int n, int first, int32_t* experts, void* out_bf16,
+               void* stream);
 
 /* ---- the general operator surface (ferrite/tensor.py:292-372, 443-485), for expressions that are not one of the
  * fused kernels above.  Strides are in elements for (batch, row, col); a stride of 0 broadcasts.  *_host arguments

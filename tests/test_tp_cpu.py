@@ -56,8 +56,8 @@ def _worker(rank, world, port, result):
 
 def _expert_worker(rank, world, port, result):
     """Expert parallelism as ferrite_b200.llama.experts does it: every rank routes every token, keeps a run of whole
-    experts (tp_keep), maps the touched experts' global ids to its own places (out of range: no expert, zeros) and
-    computes a partial sum; the all-reduce gives the one-device mixture (oracle.llama.experts)."""
+    experts (tp_keep), lists the touched experts among its own and computes a partial sum; the all-reduce gives the
+    one-device mixture (oracle.llama.experts)."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from ferrite_b200 import llama
@@ -74,11 +74,13 @@ def _expert_worker(rank, world, port, result):
     assert axis == 0 and llama.tp_keep("layers.0.experts.down", full, rank, world)[1].tolist() == kept.tolist()
     assert llama.tp_keep("layers.0.router", full, rank, world) is None
     mine_gu, mine_down = gate_up[kept], down[kept]
-    picks, weights = ollama.touched(ids, wts, E)  # global ids ascending, then E (none); weights [slots, T, 1]
-    local = np.asarray(picks).reshape(-1) - rank * len(kept)
+    # what fb_touched(first=...) lists on this rank: its own touched experts numbered from 0, other ranks' picks ignored
+    first, mine = rank * len(kept), len(kept)
+    ids_here = np.where((ids >= first) & (ids < first + mine), ids - first, mine)
+    picks, weights = ollama.touched(ids_here, wts, mine)
     partial = np.zeros((T, d))
-    for slot, e in enumerate(local):
-        if 0 <= e < len(kept):
+    for slot, e in enumerate(np.asarray(picks).reshape(-1)):
+        if e < mine:
             x = h @ mine_gu[e]
             partial += (ollama.glu(x[:, :F], x[:, F:]) * np.asarray(weights)[slot].reshape(T, 1)) @ mine_down[e]
     total = torch.from_numpy(partial.copy())

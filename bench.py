@@ -306,7 +306,8 @@ def run_ferrite(args):
         "roofline": {"bound": "hbm", "kernel": ("the whole decode step (indexed block-float matmuls + decode attention), %d tokens" if moe else
                                                 "linear_tcgen05_kernel (block-float dequant GEMM, %d tokens)") % S, "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_kind,
-                     "traffic": 1.002 * lin_bytes / lin_launches, "traffic_source": "algorithmic bytes x 1.002 (DRAM read+write of the ncu capture in profiles/, 4096x14336 bfp8, 32 tokens)",
+                     "traffic": None if moe else 1.002 * lin_bytes / lin_launches,
+                     "traffic_source": "not captured for the whole step" if moe else "algorithmic bytes x 1.002 (DRAM read+write of the ncu capture in profiles/, 4096x14336 bfp8, 32 tokens)",
                      "launches": lin_launches, "us_per_launch": lin_ms * 1e3 / lin_launches, "bytes_per_launch": lin_bytes / lin_launches},
         "step_roofline": {"algorithmic_bytes_per_gpu": whole, "frac_of_hbm": whole / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }

@@ -445,17 +445,13 @@ class Tensor:
             labels = (labels + 0).realize()
         values = Tensor(self.rt, x.rows, parts * k, batch=x.batch, dtype=x.dtype)
         ids = Tensor(self.rt, x.rows, parts * k, batch=x.batch, dtype="int32")
-        rows = x.batch * x.rows
-        for p in range(parts):  # a part is a run of columns of every row
-            off = p * cols * x.buf.element_size()
-            check(lib().fb_topk(_lib.DTYPES[x.dtype], x.buf.data_ptr() + off, rows, cols, x.cols, k, ops._ptr(labels.buf) if labels is not None else None,
-                                values.buf.data_ptr() + p * k * x.buf.element_size(), ids.buf.data_ptr() + p * k * 4, None, parts * k, ops._stream()))
-            if p:  # indices are columns of the whole row
-                pass
+        # a row of `parts` parts is `parts` rows of one part each: one launch for all of them
+        check(lib().fb_topk(_lib.DTYPES[x.dtype], x.buf.data_ptr(), x.batch * x.rows * parts, cols, cols, k, ops._ptr(labels.buf) if labels is not None else None,
+                            values.buf.data_ptr(), ids.buf.data_ptr(), None, k, ops._stream()))
         if parts > 1:
             offs = Tensor.of(self.rt, [[p * cols for p in range(parts) for _ in range(k)]], "int32")
             ids = (ids + offs).realize()
-        self.rt.launched("topk", parts)
+        self.rt.launched("topk", 1)
         return values, ids
 
     def touched(self, n, weights, first=0):

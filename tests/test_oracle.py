@@ -120,3 +120,17 @@ def test_c_restatement_equals_the_numpy_one(fmt):
         assert np.array_equal(build.bfp_values(x, fmt).astype(np.float64), g[f"{name}.{fmt}"]), name
     big = np.random.default_rng(1).normal(0, 0.02, (512, 1024)).astype(np.float32)
     assert np.array_equal(build.bfp_values(big, fmt), bfp.bfp(big, fmt).astype(np.float32))
+
+
+def test_sampling_head_restated():
+    """oracle.serve.heads against the formulas the reference's own test states (test/test_sim.py:2152-2155)."""
+    from oracle import serve as oserve
+    rng = np.random.default_rng(3)
+    x, ts = rng.normal(0, 3, (3, 512)).astype(np.float32), [1.0, 1 / 0.7, 2.0]
+    x[1, 5] = x[1, 505] = x[1].max() + 1
+    values, ids, lse = oserve.heads(x, ts)
+    want = np.argsort(-x, -1, kind="stable")[:, :64]
+    scaled = np.float64(x) * np.array(ts)[:, None]
+    exact = scaled.max(1) + np.log(np.exp(scaled - scaled.max(1, keepdims=True)).sum(1))
+    assert np.array_equal(ids, want) and np.array_equal(values, np.take_along_axis(x, want, -1)) and ids[1, 0] == 5 and ids[1, 1] == 505
+    assert np.allclose(lse[:, 0], exact, rtol=1e-12)

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this folder from the UNMODIFIED reference (alkinun/ferrite).
 
-Run in the build container only, where the reference checkout is mounted:
+Run where a checkout of the reference is at hand:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports the reference's models/gpt2.py and models/llama.py (numpy branch; nothing is compiled),
 (1) checks that the restatement under oracle/ reproduces the reference on every case (this is what
@@ -20,7 +20,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+assert len(sys.argv) > 1, "usage: make_golden.py <path to the reference checkout>"
+REF = sys.argv[1]
 sys.path[:0] = [REF, os.path.join(REF, "models"), ROOT]
 
 import gpt2  # noqa: E402  (reference)

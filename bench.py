@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama8b|smollm] [--layers L] [--impl reference]
     python bench.py --matmul 32,4096,14336,bfp8,6      (one isolated matmul, a few calls: what the ncu captures run)
+    python bench.py --attend 32,32,8,128,2048,6        (the decode attention alone, likewise)
 
 The default workload is the Llama-3.1-8B-shape batched decode (32 sequences, 2048 tokens of context each, bfp8 weights,
 bf16 KV cache), tensor-parallel over N GPUs with an NCCL all-reduce after o_proj and down_proj.  A step is one decode
@@ -56,6 +57,7 @@ def parse():
     ap.add_argument("--impl", default="ferrite_b200", choices=["ferrite_b200", "reference"])
     ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"], help="several GPUs: how the ranks' partial sums are added")
     ap.add_argument("--sweep", type=int, default=1, help="0: leave the isolated matmul sweep out of the line (a profiling run)")
+    ap.add_argument("--attend", default="", help="T,H,KV,hd,context[,calls]: only the decode attention, e.g. 32,32,8,128,2048,6")
     ap.add_argument("--matmul", default="", help="M,K,N,fmt[,calls]: only that isolated matmul (RMSNorm + SwiGLU fused), e.g. 32,4096,14336,bfp8,6")
     return ap.parse_args()
 
@@ -347,6 +349,31 @@ def one_matmul(spec):
     print(json.dumps({"matmul": spec, "calls": calls, "us_per_call_eager": e0.elapsed_time(e1) * 1e3 / calls}))
 
 
+def one_attention(spec):
+    """--attend: a few eager calls of the decode attention alone, every sequence at the same context, each call over its
+    own KV cache (four of them, together larger than L2): what an ncu capture of the kernel runs."""
+    import torch
+    from ferrite_b200 import ops
+    parts = [int(v) for v in spec.split(",")]
+    T, H, KV, hd, ctx, calls = parts[:5] + [parts[5] if len(parts) > 5 else 6]
+    device, gen = torch.device("cuda:0"), torch.Generator(device="cuda:0").manual_seed(0)
+    part = ctx + 64 - ctx % 64
+    caches = [torch.empty(2 * KV, T * part, hd, device=device, dtype=torch.bfloat16).normal_(0, 1, generator=gen) for _ in range(4)]
+    q = torch.randn(T, H * hd, device=device, generator=gen).bfloat16()
+    base = torch.arange(T, device=device, dtype=torch.int32) * part
+    place = torch.full((T,), ctx - 1, device=device, dtype=torch.int32)
+    out = torch.empty(T, H * hd, device=device, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(calls):
+        ops.decode_attention(q, caches[i % 4], base, place, H, KV, hd, ctx, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    kv_bytes = T * ctx * 2 * KV * hd * 2
+    print(json.dumps({"attend": spec, "calls": calls, "us_per_call_eager": e0.elapsed_time(e1) * 1e3 / calls, "kv_bytes_per_call": kv_bytes}))
+
+
 def matmul_sweep(device, peak_gbs, calls=200):
     """BASELINE.json configs[1]: the isolated block-float matmul, RMSNorm prologue and SwiGLU epilogue fused, K = 4096,
     M in {1, 8, 32, 128}, N in {4096, 14336}, bfp8 and bfp4.  `calls` back-to-back calls (one recorded graph) rotate
@@ -465,5 +492,7 @@ if __name__ == "__main__":
     a = parse()
     if a.matmul:
         one_matmul(a.matmul)
+    elif a.attend:
+        one_attention(a.attend)
     else:
         run_reference(a) if a.impl == "reference" else run_ferrite(a)

@@ -56,6 +56,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="fewer blocks than the model has (a smoke run; the JSON line says so)")
     ap.add_argument("--impl", default="ferrite_b200", choices=["ferrite_b200", "reference"])
     ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"], help="several GPUs: how the ranks' partial sums are added")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "bfp8", "bfp4"], help="the KV cache's format (BASELINE.json's configs keep it in bf16)")
     ap.add_argument("--sweep", type=int, default=1, help="0: leave the isolated matmul sweep out of the line (a profiling run)")
     ap.add_argument("--attend", default="", help="T,H,KV,hd,context[,calls]: only the decode attention, e.g. 32,32,8,128,2048,6")
     ap.add_argument("--matmul", default="", help="M,K,N,fmt[,calls]: only that isolated matmul (RMSNorm + SwiGLU fused), e.g. 32,4096,14336,bfp8,6")
@@ -119,13 +120,13 @@ def linear_bytes(c, sequences, fmt_bytes=1.0625, expert_bytes=None):
     return c.layers * per_layer + head, launches * c.layers + 1
 
 
-def step_bytes(c, sequences, context_rows, expert_bytes=None):
+def step_bytes(c, sequences, context_rows, expert_bytes=None, kv_bytes=2.0):
     """Algorithmic bytes a decode step reads per GPU: weights once, the KV rows each token sees (context_rows: their sum
     over the sequences), its embedding row."""
     hd = c.head_dim or c.dim // c.heads
     weights, _ = linear_bytes(c, sequences, expert_bytes=expert_bytes)
     weights -= c.layers * 0  # (activations are part of linear_bytes; they are negligible)
-    kv = context_rows * c.layers * 2 * c.kv * hd * 2
+    kv = context_rows * c.layers * 2 * c.kv * hd * kv_bytes
     return weights + kv + sequences * c.dim * 2
 
 
@@ -179,7 +180,8 @@ def run_ferrite(args):
     for _ in range(full.layers):  # the prompts' keys and values: N(0, 1), as a prefill would have left them
         t = Tensor(rt, S * part, hd, batch=2 * c.kv)
         t.buf.normal_(0, 1, generator=gen)
-        caches.append(t)
+        caches.append(t if args.kv == "bf16" else t.cast(args.kv).realize())  # (a block-float cache: rounded as a put rounds)
+    kv_bytes = {"bf16": 2.0, "bfp8": 1.0625, "bfp4": 0.5625}[args.kv]
     slots = S if S > 1 else None
 
     def step_fn(ids, places):
@@ -292,7 +294,7 @@ def run_ferrite(args):
     ms, ms_e2e, lin_ms = times.tolist()
     peaks, peak_kind = measured_peaks()
     rows_seen = sum(ctxs) + S * (args.warmup + args.steps // 2)  # KV rows the middle step of the timed run reads
-    whole = step_bytes(c, S, rows_seen, expert_bytes)
+    whole = step_bytes(c, S, rows_seen, expert_bytes, kv_bytes)
     if moe:  # the roofline of a mixture's step as a whole: every kernel of it streams weights or KV rows
         lin_bytes, lin_launches, lin_ms = whole, int(per_step or 1), ms / args.steps
     achieved = lin_bytes / (lin_ms * 1e-3) / 1e9
@@ -301,7 +303,7 @@ def run_ferrite(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}" + (f" (attention heads) + ep{world} (experts), all-reduce after o_proj and after the experts" if moe and world > 1 else ""), "reduction": reduction, "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
-                   "weights": "random N(0, 0.02) quantised on the device", "kv": "N(0, 1) bf16 standing in for the prompts' prefill"},
+                   "weights": "random N(0, 0.02) quantised on the device", "kv": "N(0, 1) %s standing in for the prompts' prefill" % args.kv},
         "e2e": {"value": S * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S, "d2h_bytes_per_step": 4 * S, "steps": e2e_steps},
         "gpu_launches": int(per_step or 0) * args.steps,
         "clocks": clk,

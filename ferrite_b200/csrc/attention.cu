@@ -1,4 +1,4 @@
-// Decode attention over a bf16 KV cache: softmax(q k^T / sqrt(hd) + mask) v for one new token per sequence
+// Decode attention over a bf16 - or block-float - KV cache: softmax(q k^T / sqrt(hd) + mask) v for one new token per sequence
 // (models/llama.py:111-146; ferrite's one-kernel attention Tensor.attend, ferrite/tensor.py:487-516,
 // ferrite/compiler.py:1147-1170).  The mask is never materialised: each token carries the first cache row of its
 // sequence (`base`) and its place; it sees keys base .. base + place (and, with a sliding window, only the last
@@ -11,7 +11,13 @@
 //   q k^T and p v run on mma.sync m16n8k16 (bf16 in, fp32 accumulate) with an online softmax in registers.
 // Keys are split across CTAs (flash-decoding) so that few sequences still fill the GPU; a second small kernel
 // merges the splits by their running maxima, as ferrite merges its `parts` (ferrite/tensor.py:511-516).
-#include "common.cuh"
+//
+// A block-float cache (bfp8 / bfp4 keys and values, models/llama.py:127-128; the reference reads it in place too,
+// test/test_sim.py:2081-2107) is a packed matrix [rows, hd] per head: a 64-key tile is one unit of each 64-column group,
+// i.e. one or two contiguous pieces of 4352 (2304) bytes.  They are staged raw by cp.async (double-buffered), unpacked
+// into the same swizzled bf16 tiles the bf16 cache is copied into, and everything after that is shared - so the result
+// is bit for bit that of a bf16 cache holding the same values, with half (a quarter) of the bytes read.
+#include "bfp_format.cuh"
 
 namespace fb {
 
@@ -35,6 +41,9 @@ struct AttnArgs {
   float* part_o;   // [entries * row tiles, splits, 16, hd]
   float* part_ml;  // [entries * row tiles, splits, 16, 2]
   int splits;
+  // block-float cache: k and v point at head 0's packed matrices (bytes), kv_s0 / kv_s1 are in bytes, and a key's
+  // cache row is base[e0] + its number, with base[e0] and the split's first key multiples of 64
+  int64_t kv_rows;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -62,15 +71,19 @@ constexpr int ATT_THREADS = 128, KEY_TILE = 64;
 template <int HD>
 __device__ __forceinline__ uint32_t tile_off(int r, int ch) { return (uint32_t)(r * HD * 2 + ((ch ^ (r & 7)) << 4)); }
 
-template <int HD>
+// KVF: 0 for a bf16 cache, FB_BFP8 / FB_BFP4 for a packed one
+template <int HD, int KVF>
 __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs a) {
   griddep_launch_dependents();
   constexpr int CH = HD / 8;               // 16-byte chunks per row
   constexpr int TILE_BYTES = KEY_TILE * HD * 2;
+  constexpr bool PACKED = KVF != 0;
+  constexpr int GROUPS = HD / 64, UNIT = PACKED ? unit_bytes(KVF) : 0, RAW_BYTES = GROUPS * UNIT;  // a tile's packed bytes
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* sQ = smem;                      // [16][HD] bf16
-  uint8_t* sK = sQ + 16 * HD * 2;          // 2 x [64][HD]
-  uint8_t* sV = sK + 2 * TILE_BYTES;       // 2 x [64][HD]
+  uint8_t* sK = sQ + 16 * HD * 2;          // 2 x [64][HD] (packed cache: one, unpacked into before each use)
+  uint8_t* sV = sK + (PACKED ? 1 : 2) * TILE_BYTES;
+  uint8_t* sRaw = sV + (PACKED ? 1 : 2) * TILE_BYTES;  // packed cache: 2 x (K's, then V's raw tile)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e = blockIdx.x, e0 = e / a.E1, e1 = e % a.E1, split = blockIdx.y, row0 = blockIdx.z * 16;
   const int rep = min(16, a.rows - row0);  // rows of this tile
@@ -82,7 +95,8 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     const int p = places[r * a.p_sr];
     len = max(len, p + 1), least = min(least, p);
   }
-  const int first = a.window > 0 ? max(0, least + 1 - a.window) : 0;
+  int first = a.window > 0 ? max(0, least + 1 - a.window) : 0;
+  first -= first % KEY_TILE;  // whole tiles (a packed cache's units); the window's mask hides the keys before it
   const int per = ((len - first + a.splits - 1) / a.splits + KEY_TILE - 1) / KEY_TILE * KEY_TILE;
   const int k0 = first + split * per, k1 = min(len, k0 + per);
   const int n_tiles = k1 > k0 ? (k1 - k0 + KEY_TILE - 1) / KEY_TILE : 0;
@@ -99,8 +113,24 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     lo_r[h] = a.window > 0 ? place_r[h] + 1 - a.window : 0;
   }
 
+  // packed: head matrices at k / v + byte offsets; unit u of column group g at (g * KS + u) * UNIT
+  const int64_t KS = PACKED ? ksteps_of(a.kv_rows) : 0;
+  const uint8_t* Kp = reinterpret_cast<const uint8_t*>(a.k) + e0 * a.kv_s0 + e1 * a.kv_s1;
+  const uint8_t* Vp = reinterpret_cast<const uint8_t*>(a.v) + e0 * a.kv_s0 + e1 * a.kv_s1;
+  const int64_t row_first = PACKED && a.base ? a.base[e0] : 0;
   auto load_tile = [&](int i, int buf) {
     const int key0 = k0 + i * KEY_TILE;
+    if (PACKED) {
+      const int64_t u = (row_first + key0) / KEY_TILE;
+      constexpr int PIECES = RAW_BYTES / 16;
+      for (int c = tid; c < 2 * PIECES; c += ATT_THREADS) {
+        const int which = c / PIECES, piece = c % PIECES, g = piece / (UNIT / 16), at = piece % (UNIT / 16);
+        const uint8_t* src = (which ? Vp : Kp) + (g * KS + u) * UNIT + at * 16;
+        cp_async16(smem_addr(sRaw + (buf * 2 + which) * RAW_BYTES) + piece * 16, src);
+      }
+      cp_async_commit();
+      return;
+    }
     for (int c = tid; c < KEY_TILE * CH; c += ATT_THREADS) {
       const int r = c / CH, ch = c % CH;
       const int key = min(key0 + r, k1 - 1);  // rows past the end repeat the last key; their scores are masked
@@ -136,7 +166,23 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     if (i + 1 < n_tiles) load_tile(i + 1, buf ^ 1);
     if (i + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
-    const uint32_t kt_base = smem_addr(sK + buf * TILE_BYTES), vt_base = smem_addr(sV + buf * TILE_BYTES);
+    if (PACKED) {  // raw -> bf16 tiles: a thread per run of 16 (16 bytes + its exponent -> two swizzled 16-byte chunks)
+      constexpr int RUNS = HD / 16;
+      for (int c = tid; c < 2 * KEY_TILE * RUNS; c += ATT_THREADS) {
+        const int which = c / (KEY_TILE * RUNS), run = (c / KEY_TILE) % RUNS, r = c % KEY_TILE;
+        const uint8_t* unit = sRaw + (buf * 2 + which) * RAW_BYTES + (run / GROUP_RUNS) * UNIT;
+        const int at = (run % GROUP_RUNS) * KSTEP + r;
+        const uint32_t top = unit[unit_mant_bytes(KVF) + at];
+        uint32_t v[8];
+        if (KVF == FB_BFP8) unpack_run8(*reinterpret_cast<const uint4*>(unit + at * 16), top, v);
+        else unpack_run4(*reinterpret_cast<const uint2*>(unit + at * 8), top, v);
+        uint8_t* tile = which ? sV : sK;
+        *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * run)) = make_uint4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * run + 1)) = make_uint4(v[4], v[5], v[6], v[7]);
+      }
+      __syncthreads();
+    }
+    const uint32_t kt_base = smem_addr(sK + (PACKED ? 0 : buf) * TILE_BYTES), vt_base = smem_addr(sV + (PACKED ? 0 : buf) * TILE_BYTES);
     const int krow = 16 * warp;  // this warp's 16 keys of the tile
 
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -201,8 +247,8 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
-  float* so = reinterpret_cast<float*>(sK);           // [4][16][HD]
-  float* sml = reinterpret_cast<float*>(sV);          // [4][16][2]
+  float* so = reinterpret_cast<float*>(sK);           // [4][16][HD]: two tiles' room (packed cache: K's tile and V's)
+  float* sml = reinterpret_cast<float*>(PACKED ? sRaw : sV);  // [4][16][2]
 #pragma unroll
   for (int dt = 0; dt < HD / 8; ++dt) {
     const int col = dt * 8 + (lane & 3) * 2, r = lane >> 2;
@@ -270,7 +316,16 @@ static size_t attention_workspace(int64_t entries, int rows, int hd, int64_t max
   return splits == 1 ? 0 : (size_t)ctas * splits * 16 * (hd + 2) * sizeof(float);
 }
 
-static int launch_attention(AttnArgs a, int64_t entries, int hd, int64_t max_keys, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+template <int HD, int KVF>
+static void launch_one(const AttnArgs& a, dim3 grid, int splits, int64_t entries, cudaStream_t s) {
+  const size_t smem = KVF ? (size_t)(16 + 2 * KEY_TILE) * HD * 2 + 4 * (HD / 64) * unit_bytes(KVF ? KVF : FB_BFP8) : (size_t)(16 + 4 * KEY_TILE) * HD * 2;
+  static bool once = false;
+  if (!once) cudaFuncSetAttribute(decode_attention_kernel<HD, KVF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
+  decode_attention_kernel<HD, KVF><<<grid, ATT_THREADS, smem, s>>>(a);
+  if (splits > 1) attention_combine_kernel<HD><<<(unsigned)(entries * a.rows), HD, 0, s>>>(a);
+}
+
+static int launch_attention(AttnArgs a, int64_t entries, int hd, int64_t max_keys, void* workspace, size_t workspace_bytes, cudaStream_t s, int kv_fmt = 0) {
   int splits;
   const size_t need = attention_workspace(entries, a.rows, hd, max_keys, &splits);
   if (need && (!workspace || workspace_bytes < need)) {
@@ -282,17 +337,14 @@ static int launch_attention(AttnArgs a, int64_t entries, int hd, int64_t max_key
   a.part_o = (float*)workspace;
   a.part_ml = (float*)workspace + (size_t)entries * tiles * splits * 16 * hd;
   dim3 grid((unsigned)entries, (unsigned)splits, (unsigned)tiles);
-  const size_t smem = (size_t)(16 + 4 * KEY_TILE) * hd * 2;
   if (hd == 128) {
-    static bool once = false;
-    if (!once) cudaFuncSetAttribute(decode_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
-    decode_attention_kernel<128><<<grid, ATT_THREADS, smem, s>>>(a);
-    if (splits > 1) attention_combine_kernel<128><<<(unsigned)(entries * a.rows), 128, 0, s>>>(a);
+    if (kv_fmt == FB_BFP8) launch_one<128, FB_BFP8>(a, grid, splits, entries, s);
+    else if (kv_fmt == FB_BFP4) launch_one<128, FB_BFP4>(a, grid, splits, entries, s);
+    else launch_one<128, 0>(a, grid, splits, entries, s);
   } else {
-    static bool once = false;
-    if (!once) cudaFuncSetAttribute(decode_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
-    decode_attention_kernel<64><<<grid, ATT_THREADS, smem, s>>>(a);
-    if (splits > 1) attention_combine_kernel<64><<<(unsigned)(entries * a.rows), 64, 0, s>>>(a);
+    if (kv_fmt == FB_BFP8) launch_one<64, FB_BFP8>(a, grid, splits, entries, s);
+    else if (kv_fmt == FB_BFP4) launch_one<64, FB_BFP4>(a, grid, splits, entries, s);
+    else launch_one<64, 0>(a, grid, splits, entries, s);
   }
   return launch_status("attention");
 }
@@ -321,6 +373,28 @@ extern "C" int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H
   a.E1 = KV, a.rows = rep, a.window = window, a.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   a.out = (uint16_t*)out, a.o_s0 = ld_o, a.o_s1 = (int64_t)rep * hd, a.o_sr = hd;
   return fb::launch_attention(a, T * KV, hd, max_keys, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int fb_decode_attention_packed(int cache_fmt, const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache_packed,
+                                          int64_t cache_rows, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out,
+                                          int64_t ld_o, void* workspace, size_t workspace_bytes, void* stream) {
+  FB_REQUIRE(cache_fmt == FB_BFP8 || cache_fmt == FB_BFP4, "fb_decode_attention_packed: a bfp8 or bfp4 cache (dtype %d given)", cache_fmt);
+  FB_REQUIRE(q && cache_packed && base && place && out && T >= 1, "fb_decode_attention_packed: null pointer or no tokens");
+  FB_REQUIRE(hd == 64 || hd == 128, "fb_decode_attention_packed: heads of 64 or 128 columns (got %d)", hd);
+  FB_REQUIRE(KV >= 1 && H % KV == 0 && H / KV <= 16, "fb_decode_attention_packed: up to 16 query heads per key head (got %d / %d)", H, KV);
+  FB_REQUIRE(ld_q >= (int64_t)H * hd && ld_o >= (int64_t)H * hd && ld_q % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)cache_packed % 16 == 0,
+             "fb_decode_attention_packed: rows of q 16-byte aligned");
+  FB_REQUIRE(max_keys >= 1 && max_keys <= cache_rows && window >= 0, "fb_decode_attention_packed: max_keys within the cache");
+  const int rep = H / KV;
+  const int64_t head_bytes = fb::packed_bytes(cache_fmt, cache_rows, hd);
+  fb::AttnArgs a{};
+  a.q = (const uint16_t*)q, a.q_s0 = ld_q, a.q_s1 = (int64_t)rep * hd, a.q_sr = hd;
+  a.k = (const uint16_t*)cache_packed, a.v = (const uint16_t*)((const uint8_t*)cache_packed + KV * head_bytes);
+  a.kv_s0 = 0, a.kv_s1 = head_bytes, a.base = base, a.kv_rows = cache_rows;
+  a.place = place, a.p_s0 = 1, a.p_s1 = 0, a.p_sr = 0;
+  a.E1 = KV, a.rows = rep, a.window = window, a.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  a.out = (uint16_t*)out, a.o_s0 = ld_o, a.o_s1 = (int64_t)rep * hd, a.o_sr = hd;
+  return fb::launch_attention(a, T * KV, hd, max_keys, workspace, workspace_bytes, (cudaStream_t)stream, cache_fmt);
 }
 
 extern "C" size_t fb_attend_workspace_bytes(int64_t entries, int64_t rows, int hd, int64_t max_keys) {

@@ -39,6 +39,43 @@ __host__ __device__ inline int bfp8_byte_of_column(int j) {  // j in 0..3 -> the
   return j == 0 ? 0 : j == 1 ? 2 : j == 2 ? 1 : 3;
 }
 
+// Round a run of 16 bf16 values (their bits) to the block float and store it as run b of row k of the packed matrix at
+// `base` (K rows).  Integer arithmetic only; bit-exact with the reference's numpy model (models/gpt2.py:21-32): the
+// largest biased exponent is shared, magnitudes are the mantissas (hidden one included) shifted down to it and
+// rounded half up into 7 bits (bfp8) or to the nearest 3 bits, ties up (bfp4); a zero carries no sign.
+template <int FMT>
+__device__ __forceinline__ void store_run(const uint32_t bits[16], uint8_t* base, int64_t K, int64_t b, int64_t k) {
+  uint32_t top = 0;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) top = max(top, (bits[j] >> 7) & 255u);
+  base[exp_offset(FMT, K, b, k)] = (uint8_t)top;
+  if (FMT == FB_BFP8) {
+    uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t e = (bits[j] >> 7) & 255u, m = (bits[j] & 127u) | (e ? 128u : 0u);
+      uint32_t shift = min(top - e, 8u);
+      uint32_t q = min((m + (1u << shift)) >> (shift + 1), 127u);
+      uint32_t sign = q ? bits[j] >> 15 : 0u;
+      const int at = bfp8_byte_of_column(j & 3);  // the magnitude's byte; the sign goes on top of the next byte up
+      out[j >> 2] |= (q << (8 * at)) | (sign << (8 * ((at + 1) & 3) + 7));
+    }
+    *reinterpret_cast<uint4*>(base + mant_offset(FMT, K, b, k)) = make_uint4(out[0], out[1], out[2], out[3]);
+  } else {
+    uint32_t out[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t e = (bits[j] >> 7) & 255u, m = (bits[j] & 127u) | (e ? 128u : 0u);
+      uint32_t shift = min(top - e, 8u);
+      uint32_t q = shift < 4 ? min((m + (16u << shift)) >> (shift + 5), 7u) : 0u;
+      uint32_t sign = q ? bits[j] >> 15 : 0u;
+      const int at = bfp4_nibble_of_column(j & 7);  // the magnitude's nibble; the sign tops the nibble three up
+      out[j >> 3] |= (q << (4 * at)) | (sign << (4 * ((at + 3) & 7) + 3));
+    }
+    *reinterpret_cast<uint2*>(base + mant_offset(FMT, K, b, k)) = make_uint2(out[0], out[1]);
+  }
+}
+
 // The unpack never converts integers to floats and never touches the sign.  A magnitude sitting in the mantissa
 // field of a bf16 whose exponent field is zero IS a number: the subnormal mag * 2^-133.  The block float's value is
 // +-mag * 2^(top-133) (models/gpt2.py:31-32), i.e. that subnormal times 2^top: two exact packed multiplications by

@@ -1,7 +1,7 @@
 // The small kernels of a decode step around the matmuls and attention: embedding gather, RoPE + KV-cache write,
 // RMSNorm on its own, greedy argmax.  All are bandwidth-trivial; they exist so a whole step stays on the device
 // (one CUDA graph) with places and ids as data, as ferrite's replayed step has them (ferrite/tensor.py:788-810).
-#include "common.cuh"
+#include "bfp_format.cuh"
 
 namespace fb {
 
@@ -34,6 +34,10 @@ struct RopeArgs {
   uint16_t* cache;  // [2 KV, cache_rows, hd], heads head_stride elements apart
   int64_t head_stride;
   int H, KV, hd;
+  // a block-float cache (Tensor.put into a bfp8 / bfp4 tensor, ferrite/compiler.py:1648-1662): 2 KV packed matrices
+  // [cache_rows, hd] one after another; each run of 16 of a row rounded as the cast rounds it
+  int cache_fmt;  // 0: bf16
+  int64_t cache_rows;
 };
 
 __global__ void rope_kv_kernel(RopeArgs a) {
@@ -61,6 +65,21 @@ __global__ void rope_kv_kernel(RopeArgs a) {
     const float s1 = bf16_bits_to_float(a.sin[at + d]), s2 = bf16_bits_to_float(a.sin[at + d + half]);
     y1 = x1 * c1 - x2 * s1;
     y2 = x2 * c2 + x1 * s2;
+  }
+  if (h >= a.H && a.cache_fmt) {  // a key or value row into the block-float cache: a thread per run of 16 rounds and stores it
+    __shared__ uint16_t row[512];
+    row[d] = (uint16_t)float_to_bf16_bits(y1);
+    row[d + half] = (uint16_t)float_to_bf16_bits(y2);
+    __syncthreads();
+    if (d < a.hd / 16) {
+      uint32_t bits[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) bits[j] = row[16 * d + j];
+      uint8_t* base = reinterpret_cast<uint8_t*>(a.cache) + (int64_t)(h - a.H) * packed_bytes(a.cache_fmt, a.cache_rows, a.hd);
+      if (a.cache_fmt == FB_BFP8) store_run<FB_BFP8>(bits, base, a.cache_rows, d, a.rows[t]);
+      else store_run<FB_BFP4>(bits, base, a.cache_rows, d, a.rows[t]);
+    }
+    return;
   }
   uint16_t* out;
   if (h < a.H) out = a.q_out + t * a.ld_q + (int64_t)h * a.hd;
@@ -165,9 +184,23 @@ extern "C" int fb_rope_kv_write(const void* qkv, int64_t T, int64_t ld_qkv, int 
   FB_REQUIRE(cache_head_stride >= cache_rows * hd, "fb_rope_kv_write: heads at least cache_rows rows apart");
   FB_REQUIRE(table_cols == hd || table_cols == (int64_t)(H + 2 * KV) * hd, "fb_rope_kv_write: tables one head wide, or as wide as q, k and v");
   fb::RopeArgs a{(const uint16_t*)qkv, ld_qkv, (const uint16_t*)cos, (const uint16_t*)sin, table_cols, places, rows,
-                 (const uint16_t*)qk_norm, eps, (uint16_t*)q_out, ld_q, (uint16_t*)cache, cache_head_stride, H, KV, hd};
+                 (const uint16_t*)qk_norm, eps, (uint16_t*)q_out, ld_q, (uint16_t*)cache, cache_head_stride, H, KV, hd, 0, cache_rows};
   fb::rope_kv_kernel<<<dim3((unsigned)T, (unsigned)(H + 2 * KV)), hd / 2, 0, (cudaStream_t)stream>>>(a);
   return fb::launch_status("fb_rope_kv_write");
+}
+
+extern "C" int fb_rope_kv_write_packed(int cache_fmt, const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos,
+                                       const void* sin, int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm,
+                                       float eps, void* q_out, int64_t ld_q, void* cache_packed, int64_t cache_rows, void* stream) {
+  FB_REQUIRE(cache_fmt == FB_BFP8 || cache_fmt == FB_BFP4, "fb_rope_kv_write_packed: a bfp8 or bfp4 cache (dtype %d given)", cache_fmt);
+  FB_REQUIRE(qkv && cos && sin && places && rows && q_out && cache_packed, "fb_rope_kv_write_packed: null pointer");
+  FB_REQUIRE(T >= 1 && H >= 1 && KV >= 1 && hd >= 16 && hd % 16 == 0 && hd <= 512 && cache_rows >= 1, "fb_rope_kv_write_packed: heads of whole runs of 16, up to 512 wide");
+  FB_REQUIRE(table_cols == hd || table_cols == (int64_t)(H + 2 * KV) * hd, "fb_rope_kv_write_packed: tables one head wide, or as wide as q, k and v");
+  FB_REQUIRE((uintptr_t)cache_packed % 16 == 0, "fb_rope_kv_write_packed: misaligned cache");
+  fb::RopeArgs a{(const uint16_t*)qkv, ld_qkv, (const uint16_t*)cos, (const uint16_t*)sin, table_cols, places, rows,
+                 (const uint16_t*)qk_norm, eps, (uint16_t*)q_out, ld_q, (uint16_t*)cache_packed, 0, H, KV, hd, cache_fmt, cache_rows};
+  fb::rope_kv_kernel<<<dim3((unsigned)T, (unsigned)(H + 2 * KV)), hd / 2, 0, (cudaStream_t)stream>>>(a);
+  return fb::launch_status("fb_rope_kv_write_packed");
 }
 
 extern "C" int fb_rmsnorm(const void* x, int64_t rows, int64_t cols, int64_t ldx, const void* w, float eps, void* out, int64_t ldo,

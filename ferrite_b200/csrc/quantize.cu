@@ -27,36 +27,7 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ src, uint8_t* __res
   int64_t b = idx % NB, k = (idx / NB) % K, mat = idx / (NB * K);
   uint32_t bits[16];
   load_run_bits(src + (mat * K + k) * N + 16 * b, bits);
-  uint32_t top = 0;
-#pragma unroll
-  for (int j = 0; j < 16; ++j) top = max(top, (bits[j] >> 7) & 255u);
-  uint8_t* base = dst + mat * packed_bytes(FMT, K, N);
-  base[exp_offset(FMT, K, b, k)] = (uint8_t)top;
-  if (FMT == FB_BFP8) {
-    uint32_t out[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      uint32_t e = (bits[j] >> 7) & 255u, m = (bits[j] & 127u) | (e ? 128u : 0u);
-      uint32_t shift = min(top - e, 8u);
-      uint32_t q = min((m + (1u << shift)) >> (shift + 1), 127u);
-      uint32_t sign = q ? bits[j] >> 15 : 0u;  // a zero carries no sign
-      const int at = bfp8_byte_of_column(j & 3);  // the magnitude's byte; the sign goes on top of the next byte up
-      out[j >> 2] |= (q << (8 * at)) | (sign << (8 * ((at + 1) & 3) + 7));
-    }
-    *reinterpret_cast<uint4*>(base + mant_offset(FMT, K, b, k)) = make_uint4(out[0], out[1], out[2], out[3]);
-  } else {
-    uint32_t out[2] = {0, 0};
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      uint32_t e = (bits[j] >> 7) & 255u, m = (bits[j] & 127u) | (e ? 128u : 0u);
-      uint32_t shift = min(top - e, 8u);
-      uint32_t q = shift < 4 ? min((m + (16u << shift)) >> (shift + 5), 7u) : 0u;
-      uint32_t sign = q ? bits[j] >> 15 : 0u;
-      const int at = bfp4_nibble_of_column(j & 7);  // the magnitude's nibble; the sign tops the nibble three up
-      out[j >> 3] |= (q << (4 * at)) | (sign << (4 * ((at + 3) & 7) + 3));
-    }
-    *reinterpret_cast<uint2*>(base + mant_offset(FMT, K, b, k)) = make_uint2(out[0], out[1]);
-  }
+  store_run<FMT>(bits, dst + mat * packed_bytes(FMT, K, N), K, b, k);
 }
 
 // (top, sign, mag) of column j of a run, from the packed bytes

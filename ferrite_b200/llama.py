@@ -270,7 +270,7 @@ def zeros(rt, dtype="bf16"):
     """zeros of a shape on the device, for kv_cache (models/llama.py:656-658)."""
     def make(shape, d=None):
         t = Tensor(rt, shape[1], shape[2], batch=shape[0], dtype=dtype)
-        t.buf.zero_()
+        (t.packed.data if dtype in BFP else t.buf).zero_()  # (a block float of zero bytes is zeros)
         return t
     return make
 

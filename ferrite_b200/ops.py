@@ -118,9 +118,18 @@ def gather_rows(table, ids, out=None):
 
 def rope_kv_write(qkv, cos, sin, places, rows, cache, H, KV, hd, q_out=None, qk_norm=None, eps=1e-5):
     """RoPE (and Qwen3's q/k norm) on a fused qkv [T, (H+2KV)*hd]; q -> q_out [T, H*hd], k and v into cache
-    [2*KV, cache_rows, hd] at rows."""
+    [2*KV, cache_rows, hd] at rows (a bf16 tensor, or a Packed block-float batch of 2*KV matrices [cache_rows, hd])."""
     T = qkv.shape[0]
     assert qkv.dtype == torch.bfloat16 and qkv.shape[1] == (H + 2 * KV) * hd and qkv.stride(1) == 1
+    if isinstance(cache, Packed):
+        assert cache.batch == 2 * KV and cache.N == hd and places.dtype == torch.int32 and rows.dtype == torch.int32
+        if q_out is None:
+            q_out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=qkv.device)
+        check(lib().fb_rope_kv_write_packed(cache.code, qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1],
+                                            places.data_ptr(), rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0),
+                                            cache.data.data_ptr(), cache.K, _stream()))
+        count()
+        return q_out
     assert cache.dtype == torch.bfloat16 and cache.shape[0] == 2 * KV and cache.shape[2] == hd and cache.stride(2) == 1 and cache.stride(1) == hd
     assert places.dtype == torch.int32 and rows.dtype == torch.int32 and places.numel() == T and rows.numel() == T
     assert cos.shape == sin.shape and cos.is_contiguous() and sin.is_contiguous() and cos.dtype == torch.bfloat16
@@ -138,7 +147,9 @@ _ATT_WS = {}
 def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=None):
     """One token per sequence: token t attends cache rows base[t] .. base[t] + place[t] of its kv head."""
     T = q.shape[0]
-    assert q.dtype == torch.bfloat16 and q.shape[1] == H * hd and q.stride(1) == 1 and cache.stride(2) == 1 and cache.stride(1) == hd
+    packed = isinstance(cache, Packed)  # a block-float cache: sequences start at multiples of 64 rows (base)
+    assert q.dtype == torch.bfloat16 and q.shape[1] == H * hd and q.stride(1) == 1
+    assert (cache.batch == 2 * KV and cache.N == hd) if packed else (cache.stride(2) == 1 and cache.stride(1) == hd)
     assert base.dtype == torch.int32 and place.dtype == torch.int32 and base.numel() == T and place.numel() == T
     if out is None:
         out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=q.device)
@@ -146,8 +157,14 @@ def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=N
     ws = _ATT_WS.get(q.device)
     if need and (ws is None or ws.numel() < need):
         ws = _ATT_WS[q.device] = torch.empty(need, dtype=torch.uint8, device=q.device)
-    check(lib().fb_decode_attention(q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data_ptr(), cache.shape[1], cache.stride(0), base.data_ptr(), place.data_ptr(),
-                                    max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None, ws.numel() if need else 0, _stream()))
+    if packed:
+        check(lib().fb_decode_attention_packed(cache.code, q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data.data_ptr(), cache.K, base.data_ptr(),
+                                               place.data_ptr(), max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None,
+                                               ws.numel() if need else 0, _stream()))
+    else:
+        check(lib().fb_decode_attention(q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data_ptr(), cache.shape[1], cache.stride(0), base.data_ptr(),
+                                        place.data_ptr(), max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None,
+                                        ws.numel() if need else 0, _stream()))
     count(2 if need else 1)  # the attention kernel, and the merge of its key splits
     return out
 

@@ -477,14 +477,14 @@ class Tensor:
         a row for each place, one head wide or as wide as self; places, rows: int32 rows read on the device."""
         hd = cache.cols
         qkv = self.realize()
-        assert qkv.batch == 1 and qkv.cols == (heads + 2 * kv) * hd and cache.batch == 2 * kv and cache.dtype == "bf16", \
+        assert qkv.batch == 1 and qkv.cols == (heads + 2 * kv) * hd and cache.batch == 2 * kv and cache.dtype in ("bf16",) + tuple(BFP), \
             f"{qkv.shape} into a cache {cache.shape}"
         assert places.dtype == rows.dtype == "int32" and places.cols == rows.cols == qkv.rows, "a place and a cache row per token"
         cos, sin, places, rows = (t.realize() for t in (cos, sin, places, rows))
         qb = qkv.buf[0] if qkv.buf.stride(2) == 1 else (qkv + 0).realize().buf[0]
         out = Tensor(self.rt, qkv.rows, heads * hd)
-        assert cache.buf.stride(2) == 1 and cache.buf.stride(1) == hd, "a cache's rows lie one after another"
-        ops.rope_kv_write(qb, cos.buf[0], sin.buf[0], places.buf.reshape(-1), rows.buf.reshape(-1), cache.buf, heads, kv, hd, q_out=out.buf[0],
+        assert cache.dtype in BFP or (cache.buf.stride(2) == 1 and cache.buf.stride(1) == hd), "a cache's rows lie one after another"
+        ops.rope_kv_write(qb, cos.buf[0], sin.buf[0], places.buf.reshape(-1), rows.buf.reshape(-1), cache.packed if cache.dtype in BFP else cache.buf, heads, kv, hd, q_out=out.buf[0],
                           qk_norm=None if qk_norm is None else qk_norm.realize().buf, eps=eps)
         self.rt.launched("rope put")
         return out
@@ -501,7 +501,8 @@ class Tensor:
         assert q.batch == 1 and q.cols % hd == 0 and heads % kv == 0 and cache.batch == 2 * kv, f"{q.shape} over a cache {cache.shape}"
         base, last = base.realize(), last.realize()
         out = Tensor(self.rt, q.rows, q.cols)
-        ops.decode_attention(q.buf[0], cache.buf, base.buf.reshape(-1), last.buf.reshape(-1), heads, kv, hd, max_keys=min(length or cache.rows, cache.rows),
+        ops.decode_attention(q.buf[0], cache.packed if cache.dtype in BFP else cache.buf, base.buf.reshape(-1), last.buf.reshape(-1), heads, kv, hd,
+                             max_keys=min(length or cache.rows, cache.rows),
                              window=window or 0, out=out.buf[0])
         self.rt.launched("attention")
         return out

@@ -156,6 +156,19 @@ int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, i
                         int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out, int64_t ld_o,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same two calls over a block-float KV cache (a cache in bfp8 or bfp4: models/llama.py:80,127-128; Tensor.put into a
+ * block-float tensor, ferrite/compiler.py:1648-1662; pinned by test/test_sim.py:2081-2107): cache_packed holds 2 KV packed
+ * matrices [cache_rows, hd] (fb_packed_bytes each), the keys' heads then the values'.  fb_rope_kv_write_packed rounds
+ * each run of 16 of a new row exactly as fb_quantize does; fb_decode_attention_packed unpacks the rows it reads to the
+ * same bf16 values a bf16 cache would hold and then computes what fb_decode_attention computes, bit for bit.
+ * base[t] (a sequence's first cache row) must be a multiple of 64: a sequence's rows start a packed unit. */
+int fb_rope_kv_write_packed(int cache_fmt, const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos, const void* sin,
+                            int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps, void* q_out,
+                            int64_t ld_q, void* cache_packed, int64_t cache_rows, void* stream);
+int fb_decode_attention_packed(int cache_fmt, const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache_packed,
+                               int64_t cache_rows, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out,
+                               int64_t ld_o, void* workspace, size_t workspace_bytes, void* stream);
+
 /* fb_decode_attention for callers that cannot provide a workspace and must not have one allocated for them (a
  * process whose own pool owns all device memory, a binding with no way to hold a scratch buffer).  It has no
  * counterpart in the reference.  The partial sums of the key splits go into an array built into the library

@@ -147,7 +147,8 @@ def attention(h, p, c, cos, sin, mask, cache, rows, slots=None):
         qkv = qkv * np.where(p["qk_on"], r * p["qk_norm"], 1)
     qkv = qkv * split_heads(cos, nh) + rotate_half(qkv) * split_heads(sin, nh)
     flat = merge_heads(qkv)
-    cache[:, list(rows)] = qkv[H:]  # this call's keys and values, at once (llama.py:126-128)
+    kv = qkv[H:]  # this call's keys and values, at once; a block-float cache rounds them (llama.py:126-128)
+    cache[:, list(rows)] = _bfp.bfp(kv, c.cache) if getattr(c, "cache", "bf16") != "bf16" else kv
     q, k, v = qkv[:H], cache[:KV], cache[KV:]
     if slots:  # a batch entry per (kv head, sequence): its rep query heads' rows side by side (llama.py:132-135)
         t = n // slots

@@ -195,8 +195,40 @@ def make_moe():
     print("moe.npz")
 
 
+def make_kv():
+    """A block-float KV cache (models/llama.py:80, 127-128): the reference's numpy branch rounds what it caches with
+    gpt2.bfp; the restatement's `cache` option must give the same logits."""
+    out = {}
+    fields, mode, _ = MODELS["dense_bfp8"]
+    for fmt in ("bfp8", "bfp4"):
+        oc, rc = ollama.model(**fields), llama.model(**fields)
+        oc.cache = fmt
+        rc.precision = llama.precision(rc, mode, kv=fmt)
+        assert llama.cache_format(rc) == fmt
+        raw = ollama.synthetic(oc, seed=11, norm_sigma=0.1, embed_sigma=1.0)
+        ow = ollama.arrays(raw, ollama.precision(oc, mode))
+        rw = ref_weights(rc, ow)
+        rng = np.random.default_rng(5)
+        ids, logits = [int(t) for t in rng.integers(0, oc.vocab, 5)], []
+        rkv, okv = llama.kv_cache(rc, 32, np.zeros), ollama.kv_cache(oc, 32)
+        for i in range(5):
+            new = ids if i == 0 else ids[-1:]
+            places = list(range(len(ids) - len(new), len(ids)))
+            got = llama.forward(new, places, rw, rc, rkv)
+            mine = ollama.forward(new, places, ow, oc, okv)
+            assert np.allclose(got, mine, rtol=1e-9, atol=1e-9), (fmt, i, np.abs(got - mine).max())
+            logits.append(got[0])
+            ids.append(int(got[0].argmax()))
+        for a, b in zip(rkv, okv):
+            assert np.array_equal(a, b), fmt
+        out[f"{fmt}.ids"], out[f"{fmt}.logits"] = np.int32(ids), np.stack(logits)
+        print("kv cache", fmt, "pinned")
+    np.savez_compressed(os.path.join(HERE, "kv.npz"), **out)
+
+
 if __name__ == "__main__":
     make_bfp()
     make_topk()
     make_moe()
     make_models()
+    make_kv()

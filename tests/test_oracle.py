@@ -134,3 +134,19 @@ def test_sampling_head_restated():
     exact = scaled.max(1) + np.log(np.exp(scaled - scaled.max(1, keepdims=True)).sum(1))
     assert np.array_equal(ids, want) and np.array_equal(values, np.take_along_axis(x, want, -1)) and ids[1, 0] == 5 and ids[1, 1] == 505
     assert np.allclose(lse[:, 0], exact, rtol=1e-12)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_block_float_kv_cache_matches_reference_vectors(fmt):
+    """The restatement with a block-float KV cache (models/llama.py:127-128) against the reference's logits."""
+    import copy
+    g = golden("kv.npz")
+    c, _, w, _ = golden_model("dense_bfp8")
+    c = copy.copy(c)
+    c.cache = fmt
+    ids, want, kv = g[f"{fmt}.ids"].tolist(), g[f"{fmt}.logits"], llama.kv_cache(c, 32)
+    for i in range(5):
+        new = ids[:5] if i == 0 else ids[4 + i:5 + i]
+        places = list(range(5)) if i == 0 else [4 + i]
+        got = llama.forward(new, places, w, c, kv)
+        assert np.allclose(got[0], want[i], rtol=1e-9, atol=1e-9), (fmt, i)

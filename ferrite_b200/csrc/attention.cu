@@ -166,10 +166,12 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     if (i + 1 < n_tiles) load_tile(i + 1, buf ^ 1);
     if (i + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
-    if (PACKED) {  // raw -> bf16 tiles: a thread per run of 16 (16 bytes + its exponent -> two swizzled 16-byte chunks)
+    if (PACKED) {
+      // raw -> bf16 tiles, each warp the 16 keys it multiplies (no other warp reads them: a warp-level sync is enough):
+      // a lane per run of 16 (16 bytes + its exponent -> two swizzled 16-byte chunks)
       constexpr int RUNS = HD / 16;
-      for (int c = tid; c < 2 * KEY_TILE * RUNS; c += ATT_THREADS) {
-        const int which = c / (KEY_TILE * RUNS), run = (c / KEY_TILE) % RUNS, r = c % KEY_TILE;
+      for (int c = lane; c < 2 * 16 * RUNS; c += 32) {
+        const int which = c / (16 * RUNS), run = (c / 16) % RUNS, r = 16 * warp + c % 16;
         const uint8_t* unit = sRaw + (buf * 2 + which) * RAW_BYTES + (run / GROUP_RUNS) * UNIT;
         const int at = (run % GROUP_RUNS) * KSTEP + r;
         const uint32_t top = unit[unit_mant_bytes(KVF) + at];
@@ -180,7 +182,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
         *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * run)) = make_uint4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * run + 1)) = make_uint4(v[4], v[5], v[6], v[7]);
       }
-      __syncthreads();
+      __syncwarp();
     }
     const uint32_t kt_base = smem_addr(sK + (PACKED ? 0 : buf) * TILE_BYTES), vt_base = smem_addr(sV + (PACKED ? 0 : buf) * TILE_BYTES);
     const int krow = 16 * warp;  // this warp's 16 keys of the tile

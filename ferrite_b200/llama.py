@@ -261,6 +261,17 @@ def forward(ids, places, w, c, caches, slots=None, every=False, length=None):
     return h.matmul(w["embed.T"], dtype="fp32")
 
 
+def prefill(ids, w, c, caches, tokens, on):
+    """A prompt from place 0 in chunks of `tokens` (models/llama.py:498-504): a chunk's keys and values are in the caches
+    before the next chunk attends, so the scores are a chunk's rows by the places so far, never the prompt squared.
+    on: makes the int32 row tensor forward takes from a list.  Returns the logits for the token after the prompt."""
+    out = None
+    for first in range(0, len(ids), tokens):
+        chunk = list(ids[first:first + tokens])
+        out = forward(on(chunk), on(list(range(first, first + len(chunk)))), w, c, caches)
+    return out
+
+
 def kv_cache(c, size, zeros, slots=1):
     """Each block's keys' heads then its values', a row for each of size places (models/llama.py:506-514)."""
     return [zeros((2 * c.kv, size, head(c))) for _ in range(c.layers)]

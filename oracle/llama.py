@@ -272,6 +272,14 @@ def forward(ids, places, w, c, caches, slots=None, every=False):
     return (h if slots or every else h[-1:]) @ w["embed.T"]
 
 
+def prefill(ids, w, c, caches, tokens):
+    """forward over a prompt from place 0, `tokens` at a time (models/llama.py:498-504); the logits after the prompt."""
+    out = None
+    for i in range(0, len(ids), tokens):
+        out = forward(ids[i:i + tokens], list(range(i, min(i + tokens, len(ids)))), w, c, caches)
+    return out
+
+
 def kv_cache(c, size, zeros=np.zeros):
     """A [2*kv, size, hd] cache per block: keys' heads then values' (models/llama.py:506-514)."""
     return [zeros((2 * c.kv, size, head(c))) for _ in range(c.layers)]

@@ -195,6 +195,25 @@ def make_moe():
     print("moe.npz")
 
 
+def make_prefill():
+    """Chunked prefill (models/llama.py:498-504): the reference's and the restatement's agree chunk size by chunk size,
+    and the reference's logits for a 13-token prompt in chunks of 4 are kept."""
+    fields, mode, _ = MODELS["dense_bfp8"]
+    oc, rc = ollama.model(**fields), llama.model(**fields)
+    raw = ollama.synthetic(oc, seed=11, norm_sigma=0.1, embed_sigma=1.0)
+    ow = ollama.arrays(raw, ollama.precision(oc, mode))
+    rw = ref_weights(rc, ow)
+    ids = [int(t) for t in np.random.default_rng(9).integers(0, oc.vocab, 13)]
+    out = {"ids": np.int32(ids)}
+    for tokens in (1, 4, 13):
+        got = llama.prefill(ids, rw, rc, llama.kv_cache(rc, 32, np.zeros), tokens)
+        mine = ollama.prefill(ids, ow, oc, ollama.kv_cache(oc, 32), tokens)
+        assert np.allclose(got, mine, rtol=1e-9, atol=1e-9), tokens
+        out[f"logits{tokens}"] = got[0]
+    np.savez_compressed(os.path.join(HERE, "prefill.npz"), **out)
+    print("prefill pinned")
+
+
 def make_kv():
     """A block-float KV cache (models/llama.py:80, 127-128): the reference's numpy branch rounds what it caches with
     gpt2.bfp; the restatement's `cache` option must give the same logits."""
@@ -232,3 +251,4 @@ if __name__ == "__main__":
     make_moe()
     make_models()
     make_kv()
+    make_prefill()

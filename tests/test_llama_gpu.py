@@ -167,3 +167,17 @@ def test_mixture_decoders(rt):
             if not (i == 2 and u == 1):
                 ok, detail = agrees(got[u], g[f"{name}.steps"][i][u])
                 assert ok, (name, i, u, detail)
+
+
+@pytest.mark.parametrize("tokens", [4, 13])
+def test_chunked_prefill(rt, tokens):
+    """A 13-token prompt in chunks (models/llama.py:498-504) against the reference's logits for the same chunks."""
+    from ferrite_b200 import llama
+    from ferrite_b200.tensor import Tensor
+    g = golden("prefill.npz")
+    c, raw, _, _ = golden_model("dense_bfp8")
+    t = llama.upload(rt, raw, llama.precision(c, "bfp8"))
+    kv = llama.kv_cache(c, 32, llama.zeros(rt))
+    out = llama.prefill(g["ids"].tolist(), t, c, kv, tokens, lambda row: Tensor.of(rt, [row], "int32"))
+    ok, detail = agrees(llama.logits(out), g[f"logits{tokens}"])
+    assert ok, detail

@@ -150,3 +150,11 @@ def test_block_float_kv_cache_matches_reference_vectors(fmt):
         places = list(range(5)) if i == 0 else [4 + i]
         got = llama.forward(new, places, w, c, kv)
         assert np.allclose(got[0], want[i], rtol=1e-9, atol=1e-9), (fmt, i)
+
+
+def test_chunked_prefill_matches_reference_vectors():
+    g = golden("prefill.npz")
+    c, _, w, _ = golden_model("dense_bfp8")
+    for tokens in (1, 4, 13):
+        got = llama.prefill(g["ids"].tolist(), w, c, llama.kv_cache(c, 32), tokens)
+        assert np.allclose(got[0], g[f"logits{tokens}"], rtol=1e-9, atol=1e-9), tokens

@@ -103,11 +103,11 @@ __device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ col,
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float lo = __uint_as_float(v[i] << 16), hi = __uint_as_float(v[i] & 0xFFFF0000u);
+        const float2 w2 = make_float2(__uint_as_float(v[i] << 16), __uint_as_float(v[i] & 0xFFFF0000u));
 #pragma unroll
-        for (int t = 0; t < M; ++t) {
-          acc[t][2 * i] = fmaf(lo, xs[t], acc[t][2 * i]);
-          acc[t][2 * i + 1] = fmaf(hi, xs[t], acc[t][2 * i + 1]);
+        for (int t = 0; t < M; ++t) {  // two columns per instruction (packed fp32 FMA)
+          const float2 r = __ffma2_rn(w2, make_float2(xs[t], xs[t]), make_float2(acc[t][2 * i], acc[t][2 * i + 1]));
+          acc[t][2 * i] = r.x, acc[t][2 * i + 1] = r.y;
         }
       }
     }

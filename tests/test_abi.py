@@ -37,3 +37,19 @@ def test_bad_arguments_are_refused_without_a_gpu():
     assert rc == -1 and b"block float" in lib.fb_last_error()
     rc = lib.fb_linear(_lib.BFP8, 16, 1, 30, 32, 16, 32, 16, _lib.BF16, 32, None, 1e-5, 0, None, 0, None, 0, None)
     assert rc == -1 and b"multiple of 4" in lib.fb_last_error()
+
+
+def test_new_entry_points_refuse_bad_arguments_without_a_gpu():
+    import ctypes
+    lib = _lib.lib()
+    two = (ctypes.c_void_p * 2)(16, 32)
+    rc = lib.fb_peer_reduce_add(two, two, 0, 9, 16, 64, None, 16, None)
+    assert rc == -1 and b"up to 8 ranks" in lib.fb_last_error()
+    rc = lib.fb_peer_reduce_add(two, two, 0, 2, 16, 60, None, 16, None)
+    assert rc == -1 and b"16-byte pieces" in lib.fb_last_error()
+    rc = lib.fb_rope_kv_write_packed(_lib.BF16, 16, 1, 256, 2, 1, 64, 16, 16, 64, 16, 16, None, 1e-5, 16, 128, 16, 64, None)
+    assert rc == -1 and b"bfp8 or bfp4 cache" in lib.fb_last_error()
+    rc = lib.fb_decode_attention_packed(_lib.BFP8, 16, 1, 128, 2, 1, 96, 16, 64, 16, 16, 64, 0, 16, 128, None, 0, None)
+    assert rc == -1 and b"64 or 128" in lib.fb_last_error()
+    rc = lib.fb_touched(16, 16, 4, 40, 8, 0, 16, 16, None)
+    assert rc == -1 and b"up to 32 choices" in lib.fb_last_error()

@@ -110,15 +110,26 @@ __global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ Red
   const int lane = threadIdx.x & 31;
   const int64_t c = o % a.outer[2], r = (o / a.outer[2]) % a.outer[1], b = o / (a.outer[2] * a.outer[1]);
   const int64_t start = b * a.in.s[0] + r * a.in.s[1] + c * a.in.s[2];
-  float acc = a.is_max ? -INFINITY : 0.f;
-  for (int64_t i = lane; i < a.len; i += 32) {
+  auto value = [&](int64_t i) {
     const int64_t at = start + i * a.step;
-    float v;
-    if (a.in.dtype == FB_BF16) v = bf16_bits_to_float(static_cast<const uint16_t*>(a.in.ptr)[at]);
-    else if (a.in.dtype == FB_FP32) v = static_cast<const float*>(a.in.ptr)[at];
-    else v = (float)static_cast<const int32_t*>(a.in.ptr)[at];
-    acc = a.is_max ? fmaxf(acc, v) : acc + v;
+    if (a.in.dtype == FB_BF16) return bf16_bits_to_float(static_cast<const uint16_t*>(a.in.ptr)[at]);
+    if (a.in.dtype == FB_FP32) return static_cast<const float*>(a.in.ptr)[at];
+    return (float)static_cast<const int32_t*>(a.in.ptr)[at];
+  };
+  // four loads in flight a lane (a long row is otherwise one L2 round trip per element), each with its own partial
+  float part[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) part[u] = a.is_max ? -INFINITY : 0.f;
+  int64_t i = lane;
+  for (; i + 96 < a.len; i += 128) {
+    float v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = value(i + 32 * u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) part[u] = a.is_max ? fmaxf(part[u], v[u]) : part[u] + v[u];
   }
+  for (; i < a.len; i += 32) part[0] = a.is_max ? fmaxf(part[0], value(i)) : part[0] + value(i);
+  float acc = a.is_max ? fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) : (part[0] + part[1]) + (part[2] + part[3]);
   acc = a.is_max ? warp_max(acc) : warp_sum(acc);
   if (lane == 0) {
     const int64_t at = b * a.out.s[0] + r * a.out.s[1] + c * a.out.s[2];
@@ -147,6 +158,31 @@ __global__ void __launch_bounds__(256) matmul_kernel(const __grid_constant__ Mat
     __syncthreads();
   }
   if (row < g.M && col < g.N) {
+    const int64_t at = bz * g.c.s[0] + row * g.c.s[1] + col * g.c.s[2];
+    if (g.c.dtype == FB_BF16) static_cast<uint16_t*>(const_cast<void*>(g.c.ptr))[at] = (uint16_t)float_to_bf16_bits(acc);
+    else static_cast<float*>(const_cast<void*>(g.c.ptr))[at] = acc;
+  }
+}
+
+// The same for a result of few elements and a long K (a router's logits: 64 x 8 over 4096): a warp per element of C
+// strides over K, so that the whole GPU works on it instead of a handful of tiles walking K one after another.
+__global__ void __launch_bounds__(256) matmul_skinny_kernel(const __grid_constant__ MatmulArgs g) {
+  const int64_t o = blockIdx.x * (int64_t)(blockDim.x / 32) + threadIdx.x / 32;
+  if (o >= g.batch * g.M * g.N) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t col = o % g.N, row = (o / g.N) % g.M, bz = o / (g.N * g.M);
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+  int64_t k = lane;
+  for (; k + 96 < g.K; k += 128) {
+    float x[4], y[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) x[u] = load_as_float(g.a, bz, row, k + 32 * u), y[u] = load_as_float(g.b, bz, k + 32 * u, col);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) part[u] = fmaf(x[u], y[u], part[u]);
+  }
+  for (; k < g.K; k += 32) part[0] = fmaf(load_as_float(g.a, bz, row, k), load_as_float(g.b, bz, k, col), part[0]);
+  const float acc = warp_sum((part[0] + part[1]) + (part[2] + part[3]));
+  if (lane == 0) {
     const int64_t at = bz * g.c.s[0] + row * g.c.s[1] + col * g.c.s[2];
     if (g.c.dtype == FB_BF16) static_cast<uint16_t*>(const_cast<void*>(g.c.ptr))[at] = (uint16_t)float_to_bf16_bits(acc);
     else static_cast<float*>(const_cast<void*>(g.c.ptr))[at] = acc;
@@ -210,6 +246,9 @@ extern "C" int fb_matmul(const void* a, const int64_t* a_strides_host, int a_dty
              "fb_matmul: operands are bf16 or fp32 (the FPU multiplies floats, ferrite/tensor.py:466)");
   g.batch = batch, g.M = M, g.N = N, g.K = K;
   dim3 grid((unsigned)fb::ceil_div(N, 16), (unsigned)fb::ceil_div(M, 16), (unsigned)batch);
-  fb::matmul_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(g);
+  if ((int64_t)grid.x * grid.y * grid.z < 148 && K >= 512 && batch * M * N <= 148 * 64)  // few tiles, long K: a warp per element
+    fb::matmul_skinny_kernel<<<(unsigned)fb::ceil_div(batch * M * N, 8), 256, 0, (cudaStream_t)stream>>>(g);
+  else
+    fb::matmul_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(g);
   return fb::launch_status("fb_matmul");
 }

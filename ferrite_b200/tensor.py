@@ -552,6 +552,8 @@ def _realize(t, into=None):
             return
         if _fused_linear(t, into):
             return
+        if _run_rmsnorm(t, into):
+            return
         _run_elementwise(t, into)
     elif op == "reduce_sum" and t.args["axis"] == 0 and _match_experts(t.srcs[0]):
         _run_experts(t, _match_experts(t.srcs[0]), None, into)
@@ -616,6 +618,23 @@ def _match_rms(t):
             if sq.op == "mul" and sq.srcs[0] is x and sq.srcs[1] is x:
                 return x, w, float(eps)
     return None
+
+
+def _run_rmsnorm(t, into):
+    """t as one fb_rmsnorm call where its tree is an RMSNorm of bf16 rows that no matmul takes in as its prologue (a
+    mixture's router and experts both read the normed rows; the output layer of a single sequence reads its last)."""
+    found = _match_rms(t) if t.dtype == "bf16" and t.batch == 1 else None
+    if not found or found[0].dtype != "bf16" or found[0].shape != t.shape:
+        return False
+    x, w, eps = found
+    x = x.realize()
+    if x.buf.stride(2) != 1 or (into is not None and into.buf.stride(2) != 1):
+        return False
+    out = into if into is not None else Tensor(t.rt, t.rows, t.cols)
+    ops.rmsnorm(x.buf[0], w.realize().buf.reshape(-1), eps, out=out.buf[0])
+    t.rt.launched("rmsnorm")
+    _done(t, buf=out.buf)
+    return True
 
 
 def _match_silu_of(g):

@@ -1,4 +1,4 @@
-// Bandwidth-bound block-float GEMV for a few tokens (M <= 4) on CUDA cores.
+// Block-float GEMV on CUDA cores: one token (fb_linear sends more to the tensor-core kernel; up to 4 a pass otherwise).
 //
 // Work split: one column block (16 output columns, one shared-exponent run per row k) per group of warps;
 // the group's lanes split K, each lane streaming 4 consecutive rows per step as 64 (bfp8) or 32 (bfp4)

@@ -32,7 +32,7 @@ struct IndexedArgs {
   const void* row_scale;    // mode 1: bf16 [slot * M + t] multiplying the epilogue's result, or null
 };
 
-int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: M <= 4 per pass, CUDA cores
+int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: one token (up to 4 a pass), CUDA cores
 int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores
 int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStream_t s);
 bool linear_tcgen05_supports(const LinearArgs& a);

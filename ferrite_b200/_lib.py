@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libferrite_b200.so")
 BF16, FP32, INT32, BFP8, BFP4 = 0, 1, 2, 3, 4
 DTYPES = {"bf16": BF16, "fp32": FP32, "int32": INT32, "bfp8": BFP8, "bfp4": BFP4}
 EPI_NONE, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 2
+LINEAR_AUTO, LINEAR_TCGEN05, LINEAR_GEMV, LINEAR_MMA = 0, 1, 2, 3  # fb_linear_prefer
 
 _p, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 
@@ -25,6 +26,7 @@ SIGNATURES = {
     "fb_dequantize": (_i, [_i, _p, _i64, _i64, _i64, _p, _p]),
     "fb_unpack_fields": (_i, [_i, _p, _i64, _i64, _i64, _p, _p, _p, _p]),
     "fb_linear_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fb_linear_prefer": (_i, [_i]),
     "fb_linear": (_i, [_i, _p, _i64, _i64, _i64, _p, _i64, _p, _i, _i64, _p, _f, _i, _p, _i64, _p, _sz, _p]),
     "fb_linear_indexed": (_i, [_i, _p, _i64, _i64, _i64, _i64, _p, _i64, _i, _p, _i, _i, _p, _i, _i64, _i64, _p, _f, _i, _p, _i64, _p, _p, _sz, _p]),
     "fb_gather_rows": (_i, [_p, _i64, _i64, _p, _i64, _p, _p]),

@@ -471,6 +471,29 @@ struct Plan {
   size_t smem;
 };
 
+// CTAs of the kernel that are resident at once when launched as clusters of `cluster` (asked of the driver once per
+// format and size; the largest ring is assumed - a kernel with tensor memory is alone on its SM whatever it needs)
+int resident_ctas(int fmt, int cluster) {
+  static int known[2][9] = {};
+  int* have = known[fmt == FB_BFP8];
+  if (!have[1]) {  // every size at the first call (which is not inside a stream capture: a graph's first run is eager)
+    auto kernel = fmt == FB_BFP8 ? linear_tcgen05_kernel<FB_BFP8> : linear_tcgen05_kernel<FB_BFP4>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    for (int n = 1; n <= 8; ++n) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(148, n, 1), cfg.blockDim = dim3(THREADS), cfg.dynamicSmemBytes = 200 * 1024;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = (unsigned)n, attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr, cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) clusters = 148 / n, cudaGetLastError();
+      have[n] = clusters * n;
+    }
+  }
+  return have[cluster];
+}
+
 // slots, mode: an indexed matmul's (mode 1: so many results, more CTAs; mode 2: so many times the steps of K)
 Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots = 1, int mode = 0) {
   Plan pl;
@@ -488,7 +511,9 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots
     if (epilogue == FB_EPI_SWIGLU && s != 1 && s != 2 && s != 4) continue;
     const int per = (int)ceil_div(pl.steps, s);
     if ((int)ceil_div(pl.steps, per) != s) continue;  // every split gets work
-    const double cost = (double)ceil_div(ctas_per_split * s, 148) * (5.0 + (s > 1 ? 1.0 : 0.0) + 0.6 * per);
+    // (a CTA has its SM to itself; clusters of some sizes - 3, 5, 6, 7 - do not pack the GPCs' SMs fully, and a grid
+    // of a few CTAs more than are resident together takes twice the time: ask the driver how many clusters fit)
+    const double cost = (double)ceil_div(ctas_per_split * s, resident_ctas(fmt, s)) * (5.0 + (s > 1 ? 1.0 : 0.0) + 0.6 * per);
     if (cost < best_cost) best_cost = cost, best = s;
   }
   pl.splits = best;
@@ -512,7 +537,7 @@ bool linear_tcgen05_supports(const LinearArgs& a) {
 
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N) {
   (void)N;
-  if (M <= 1) return 0;
+  if (M < 1) return 0;
   return WS_RSTD + (size_t)(M < 128 ? M : 128) * K * 2;
 }
 

@@ -33,7 +33,9 @@ struct IndexedArgs {
 };
 
 int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: one token (up to 4 a pass), CUDA cores
-int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores
+int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores (tcgen05, tiles through shared memory)
+int linear_mma(const LinearArgs& a, cudaStream_t s);      // gemm_mma.cu: up to 32 tokens, tensor cores fed from registers
+bool linear_mma_supports(const LinearArgs& a);
 int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStream_t s);
 bool linear_tcgen05_supports(const LinearArgs& a);
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N);

@@ -97,13 +97,23 @@ int fb_unpack_fields(int fmt, const void* packed, int64_t batch, int64_t K, int6
  *   acc = h @ W, fp32 accumulation, W packed [K, N] in `fmt` (FB_BFP8, FB_BFP4 or FB_BF16 row-major)
  *   epilogue (fb_epilogue), out dtype FB_BF16 or FB_FP32 (fp32: the output layer, models/llama.py:479)
  * out is [M, N] (or [M, N/2] after FB_EPI_SWIGLU), row stride ldo elements.
- * M == 1 runs as a bandwidth-bound GEMV on CUDA cores; larger M on tcgen05 tensor cores.
+ * M == 1 runs as a bandwidth-bound GEMV on CUDA cores; 2..8 rows of the smaller matrices on tensor-core MMAs whose
+ * weight fragments are unpacked in registers; the rest on tcgen05 tensor cores (weight tiles through shared memory,
+ * accumulators in TMEM).
  * workspace: fb_linear_workspace_bytes(M, K, N) bytes of device scratch (0 / NULL when that is 0):
  * it holds the normalised activations of the RMSNorm prologue between the two kernels of a call. */
 size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out,
               int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,
               int64_t ldr, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Which kernel fb_linear runs (process-wide; for measurements that compare them - results agree within the rounding
+ * stated for each).  FB_LINEAR_AUTO (the default) chooses by M as described above; FB_LINEAR_TCGEN05 and
+ * FB_LINEAR_GEMV restore the choice without the register-fed kernel (GEMV up to 4 rows when asked for, else one row);
+ * FB_LINEAR_MMA sends every shape the register-fed kernel supports (M <= 32, K a multiple of 16) to it, one row too.
+ * The reference has one matmul kernel and no such switch (ferrite/compiler.py:699-738). */
+enum fb_linear_kernel { FB_LINEAR_AUTO = 0, FB_LINEAR_TCGEN05 = 1, FB_LINEAR_GEMV = 2, FB_LINEAR_MMA = 3 };
+int fb_linear_prefer(int kernel);
 
 /* Tensor.matmul(index=) (ferrite/tensor.py:450-460; ferrite/compiler.py:704-706): a mixture of experts' matmul.  W is
  * a batch of n_experts packed [K, N] matrices fb_packed_bytes(fmt, K, N) apart; index[slot] (int32, read on the

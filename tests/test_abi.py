@@ -37,6 +37,9 @@ def test_bad_arguments_are_refused_without_a_gpu():
     assert rc == -1 and b"block float" in lib.fb_last_error()
     rc = lib.fb_linear(_lib.BFP8, 16, 1, 30, 32, 16, 32, 16, _lib.BF16, 32, None, 1e-5, 0, None, 0, None, 0, None)
     assert rc == -1 and b"multiple of 4" in lib.fb_last_error()
+    rc = lib.fb_linear_prefer(7)
+    assert rc == -1 and b"unknown kernel" in lib.fb_last_error()
+    assert lib.fb_linear_prefer(_lib.LINEAR_AUTO) == 0
 
 
 def test_new_entry_points_refuse_bad_arguments_without_a_gpu():

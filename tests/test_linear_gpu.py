@@ -66,6 +66,56 @@ def test_residual_epilogue(cuda, fmt):
     assert rel_err(got32, want) < 2e-5
 
 
+@pytest.fixture
+def prefer():
+    """fb_linear_prefer for the length of a test (the choice is process-wide)."""
+    from ferrite_b200 import _lib
+    yield lambda kernel: _lib.lib().fb_linear_prefer(getattr(_lib, "LINEAR_" + kernel))
+    _lib.lib().fb_linear_prefer(_lib.LINEAR_AUTO)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("M,K,N,norm,epilogue", [(1, 512, 256, False, "none"), (5, 48, 48, False, "none"), (8, 4096, 6144, True, "none"),
+                                                 (9, 1024, 2048, True, "swiglu"), (16, 2048, 1024, False, "residual"),
+                                                 (17, 512, 1088, False, "none"), (32, 4096, 4096, True, "swiglu"),
+                                                 (32, 14336, 512, False, "residual")])
+def test_register_fed_kernel_every_shape_it_takes(cuda, prefer, fmt, M, K, N, norm, epilogue):
+    # fb_linear chooses this kernel for 2..8 rows of the smaller matrices only; asked for by name it takes up to 32 rows,
+    # one too: 1, 2 and 4 token tiles, K slices over a cluster, a CTA whose second column group does not exist
+    # (N = 48, 1088), every epilogue - against exact products, and against the tcgen05 kernel on the same inputs
+    rng = np.random.default_rng(M + K + N)
+    x, wq, tx, packed = case(rng, M, K, N, fmt, cuda)
+    g = bfp.bf16_round(rng.normal(1, 0.1, (1, K)).astype(np.float32)) if norm else None
+    r = bfp.bf16_round(rng.normal(0, 1, (M, N)).astype(np.float32)) if epilogue == "residual" else None
+    h = llama.rms(x.astype(np.float64), g, 1e-5) if norm else x.astype(np.float64)
+    want = h @ wq
+    if epilogue == "swiglu":
+        want = llama.glu(want[:, :N // 2], want[:, N // 2:])
+    if epilogue == "residual":
+        want = want + r
+    kw = dict(out_dtype="fp32", norm_w=to_bf16_tensor(g, cuda) if norm else None, eps=1e-5, epilogue=epilogue,
+              residual=to_bf16_tensor(r, cuda) if r is not None else None)
+    prefer("MMA")
+    got = ops.linear(tx, packed, **kw)
+    again = ops.linear(tx, packed, **kw)
+    prefer("TCGEN05")
+    other = to_numpy(ops.linear(tx, packed, **kw))
+    assert torch.equal(got, again), "the K slices are added in a fixed order"
+    got = to_numpy(got)
+    tol = 4e-3 if norm else 2e-5  # with a norm the operand is the normalised activation rounded to bf16 once
+    assert rel_err(got, want) < tol
+    assert rel_err(got, other) < (tol if M > 1 else 4e-3)
+
+
+def test_register_fed_kernel_beyond_its_one_multiply_scale(cuda, prefer):
+    # shared exponents above 187 (values of 2^54 and more) take the two-multiply route; tiny runs next to them too
+    rng = np.random.default_rng(3)
+    x, wq, tx, packed = case(rng, 8, 512, 256, "bfp8", cuda, sigma=2.0 ** 60)
+    prefer("MMA")
+    got = to_numpy(ops.linear(tx, packed, out_dtype="fp32"))
+    assert rel_err(got, x.astype(np.float64) @ wq) < 2e-5
+
+
 def test_bfp_matmul_equals_the_matmul_by_its_values(cuda):
     # the reference's claim for a block-float B (test/test_sim.py:373-377): the same result as the matmul by the
     # values it holds; here: quantising the dequantised weight again changes no output bit

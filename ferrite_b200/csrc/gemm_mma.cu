@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(MTHREADS, NT == 4 ? 2 : 3) linear_mma_kernel(c
     } else {
       n = 128 * (int64_t)blockIdx.x + c;
       if (n >= a.N) continue;
-      if (a.epilogue == FB_EPI_RESIDUAL) v += bf16_bits_to_float(__ldg(static_cast<const uint16_t*>(a.residual) + tok * a.ldr + n));
+      if (a.epilogue == FB_EPI_RESIDUAL) v += bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[tok * a.ldr + n]);
     }
     if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[tok * a.ldo + n] = v;
     else static_cast<uint16_t*>(a.out)[tok * a.ldo + n] = (uint16_t)float_to_bf16_bits(v);

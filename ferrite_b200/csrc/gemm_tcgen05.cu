@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       for (int e = 0; e < 8; ++e) {  // the residual reads of the eight tokens are in flight together
         const int t = col0 + cb + e;
         res[e] = live && t < a.M && a.epilogue == FB_EPI_RESIDUAL
-                     ? bf16_bits_to_float(__ldg(static_cast<const uint16_t*>(a.residual) + t * a.ldr + n)) : 0.f;
+                     ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[t * a.ldr + n]) : 0.f;
       }
       tmem_ld8(tmem + ((uint32_t)(32 * q) << 16) + col0 + cb, v);
       if (n_steps > 1) {  // the odd steps' accumulator
@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
         res[e] = 0.f;
         if (idx < total && a.epilogue == FB_EPI_RESIDUAL) {
           const int t = (int)__umulhi((uint32_t)idx, inv_rows), n = TILE_N * tile + split * rows_per + (idx - t * out_rows);
-          if (n < a.N) res[e] = bf16_bits_to_float(__ldg(static_cast<const uint16_t*>(a.residual) + t * a.ldr + n));
+          if (n < a.N) res[e] = bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[t * a.ldr + n]);
         }
       }
 #pragma unroll

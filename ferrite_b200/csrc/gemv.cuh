@@ -49,7 +49,7 @@ __device__ __forceinline__ void unpack_row(const Raw4<FMT>& r, int kk, uint32_t 
 // acc[t][j] += sum_k x[t][k] * g[k] * W[k][16b + j];  ss[t] += sum_k x[t][k]^2 over the rows this lane reads.
 template <int FMT, int M, bool NORM>
 __device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ col, int run,
-                                                const uint16_t* __restrict__ x, int64_t ldx, const uint16_t* __restrict__ g,
+                                                const uint16_t* x, int64_t ldx, const uint16_t* __restrict__ g,
                                                 int64_t K, int64_t k_first, int64_t k_step, float acc[M][16], float ss[M]) {
   const int lane = threadIdx.x & 31;
   int64_t k0 = k_first + 4 * lane;
@@ -68,7 +68,8 @@ __device__ __forceinline__ void gemv_accumulate(const uint8_t* __restrict__ col,
     }
 #pragma unroll
     for (int t = 0; t < M; ++t) {
-      uint2 xb = __ldg(reinterpret_cast<const uint2*>(x + t * ldx + k0));
+      // (a plain load: an invariant one - __ldg - may be scheduled above griddep_wait(), whose asm it does not alias)
+      uint2 xb = *reinterpret_cast<const uint2*>(x + t * ldx + k0);
       xv[t][0] = bf16_bits_to_float(xb.x & 0xFFFFu), xv[t][1] = bf16_bits_to_float(xb.x >> 16);
       xv[t][2] = bf16_bits_to_float(xb.y & 0xFFFFu), xv[t][3] = bf16_bits_to_float(xb.y >> 16);
       if (NORM) {

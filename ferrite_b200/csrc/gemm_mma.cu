@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(MTHREADS, NT == 4 ? 2 : 3) linear_mma_kernel(c
   const uint8_t* Wp = static_cast<const uint8_t*>(a.W);
   const uint8_t* strip = Wp + (live ? my_group : 0) * KS * UNIT;  // the group's units follow each other along K
 
-  // L2 prefetch of the two strips' slices: the first stretch now, the rest as warp 0 walks (two units per step of its)
+  // L2 prefetch of the two strips' slices: the first stretch now, the rest as warp 0 walks (a unit per turn of its)
   const int u_begin = s_begin >> 2, u_end = (s_end + 3) >> 2;
   if (warp == 0 && (lane == 0 || lane == 16) && live && u_begin < u_end) {
     const int n = min(PREFETCH_UNITS, u_end - u_begin);

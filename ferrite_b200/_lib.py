@@ -31,7 +31,7 @@ SIGNATURES = {
     "fb_linear_indexed": (_i, [_i, _p, _i64, _i64, _i64, _i64, _p, _i64, _i, _p, _i, _i, _p, _i, _i64, _i64, _p, _f, _i, _p, _i64, _p, _p, _sz, _p]),
     "fb_gather_rows": (_i, [_p, _i64, _i64, _p, _i64, _p, _p]),
     "fb_put_rows": (_i, [_p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _i64, _i, _p]),
-    "fb_rope_kv_write": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _p, _i64, _p, _p, _p, _f, _p, _i64, _p, _i64, _i64, _p]),
+    "fb_rope_kv_write": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _p, _i64, _i64, _p, _p, _p, _f, _p, _i64, _p, _i64, _i64, _p]),
     "fb_decode_attention_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i64]),
     "fb_decode_attention": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _i64, _i64, _p, _p, _i64, _i, _p, _i64, _p, _sz, _p]),
     "fb_decode_attention_static_max_bytes": (_sz, []),
@@ -45,7 +45,7 @@ SIGNATURES = {
     "fb_matmul": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),
     "fb_rmsnorm": (_i, [_p, _i64, _i64, _i64, _p, _f, _p, _i64, _p]),
     "fb_argmax": (_i, [_p, _i64, _i64, _i64, _p, _p, _p]),
-    "fb_rope_kv_write_packed": (_i, [_i, _p, _i64, _i64, _i, _i, _i, _p, _p, _i64, _p, _p, _p, _f, _p, _i64, _p, _i64, _p]),
+    "fb_rope_kv_write_packed": (_i, [_i, _p, _i64, _i64, _i, _i, _i, _p, _p, _i64, _i64, _p, _p, _p, _f, _p, _i64, _p, _i64, _p]),
     "fb_decode_attention_packed": (_i, [_i, _p, _i64, _i64, _i, _i, _i, _p, _i64, _p, _p, _i64, _i, _p, _i64, _p, _sz, _p]),
     "fb_peer_reduce_add": (_i, [_p, _p, _i, _i, _p, _i64, _p, _p, _p]),
 }

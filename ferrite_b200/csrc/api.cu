@@ -26,3 +26,8 @@ int launch_status(const char* what) {
 
 extern "C" int fb_version(void) { return 1; }
 extern "C" const char* fb_last_error(void) { return fb::g_error; }
+
+extern "C" int fb_status_word(void) {
+  const int a = fb::status_word_tcgen05(), b = fb::status_word_peer();  // (both read, so both are cleared)
+  return a ? a : b;
+}

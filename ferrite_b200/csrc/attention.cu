@@ -41,6 +41,7 @@ struct AttnArgs {
   float* part_o;   // [entries * row tiles, splits, 16, hd]
   float* part_ml;  // [entries * row tiles, splits, 16, 2]
   int splits;
+  // rows a head's keys have (the cache's rows, or an entry's keys): no key at or past it is read, whatever a place says.
   // block-float cache: k and v point at head 0's packed matrices (bytes), kv_s0 / kv_s1 are in bytes, and a key's
   // cache row is base[e0] + its number, with base[e0] and the split's first key multiples of 64
   int64_t kv_rows;
@@ -95,12 +96,16 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     const int p = places[r * a.p_sr];
     len = max(len, p + 1), least = min(least, p);
   }
+  // a place past its sequence's rows (or a first row outside the cache) reads no key that is not there
+  const int64_t seq_first = a.base ? a.base[e0] : 0;
+  const int64_t room = seq_first < 0 ? 0 : a.kv_rows - seq_first;
+  len = (int)max((int64_t)0, min((int64_t)len, room));
   int first = a.window > 0 ? max(0, least + 1 - a.window) : 0;
   first -= first % KEY_TILE;  // whole tiles (a packed cache's units); the window's mask hides the keys before it
   const int per = ((len - first + a.splits - 1) / a.splits + KEY_TILE - 1) / KEY_TILE * KEY_TILE;
   const int k0 = first + split * per, k1 = min(len, k0 + per);
   const int n_tiles = k1 > k0 ? (k1 - k0 + KEY_TILE - 1) / KEY_TILE : 0;
-  const int64_t kv_off = e0 * a.kv_s0 + e1 * a.kv_s1 + (a.base ? (int64_t)a.base[e0] * HD : 0);
+  const int64_t kv_off = e0 * a.kv_s0 + e1 * a.kv_s1 + (len > 0 ? seq_first * HD : 0);
   const uint16_t* Kg = a.k + kv_off;
   const uint16_t* Vg = a.v + kv_off;
   const uint16_t* Qg = a.q + e0 * a.q_s0 + e1 * a.q_s1 + (int64_t)row0 * a.q_sr;
@@ -117,7 +122,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
   const int64_t KS = PACKED ? ksteps_of(a.kv_rows) : 0;
   const uint8_t* Kp = reinterpret_cast<const uint8_t*>(a.k) + e0 * a.kv_s0 + e1 * a.kv_s1;
   const uint8_t* Vp = reinterpret_cast<const uint8_t*>(a.v) + e0 * a.kv_s0 + e1 * a.kv_s1;
-  const int64_t row_first = PACKED && a.base ? a.base[e0] : 0;
+  const int64_t row_first = PACKED && len > 0 ? seq_first : 0;
   auto load_tile = [&](int i, int buf) {
     const int key0 = k0 + i * KEY_TILE;
     if (PACKED) {
@@ -305,6 +310,7 @@ __global__ void __launch_bounds__(HD) attention_combine_kernel(AttnArgs a) {
 }
 
 static int pick_splits(int64_t ctas, int64_t max_keys) {
+  if (ctas < 1) return 1;
   int64_t want = (4 * 148 + ctas - 1) / ctas;                           // about four CTAs per SM in flight
   const int64_t most = (max_keys + 2 * KEY_TILE - 1) / (2 * KEY_TILE);  // at least two tiles per split
   want = want > most ? most : want;
@@ -321,8 +327,8 @@ static size_t attention_workspace(int64_t entries, int rows, int hd, int64_t max
 template <int HD, int KVF>
 static void launch_one(const AttnArgs& a, dim3 grid, int splits, int64_t entries, cudaStream_t s) {
   const size_t smem = KVF ? (size_t)(16 + 2 * KEY_TILE) * HD * 2 + 4 * (HD / 64) * unit_bytes(KVF ? KVF : FB_BFP8) : (size_t)(16 + 4 * KEY_TILE) * HD * 2;
-  static bool once = false;
-  if (!once) cudaFuncSetAttribute(decode_attention_kernel<HD, KVF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), once = true;
+  static std::atomic<uint64_t> opted{0};  // the shared-memory opt-in, once per device
+  if (first_on_device(opted)) cudaFuncSetAttribute(decode_attention_kernel<HD, KVF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   decode_attention_kernel<HD, KVF><<<grid, ATT_THREADS, smem, s>>>(a);
   if (splits > 1) attention_combine_kernel<HD><<<(unsigned)(entries * a.rows), HD, 0, s>>>(a);
 }
@@ -354,6 +360,7 @@ static int launch_attention(AttnArgs a, int64_t entries, int hd, int64_t max_key
 }  // namespace fb
 
 extern "C" size_t fb_decode_attention_workspace_bytes(int64_t T, int H, int KV, int hd, int64_t max_keys) {
+  if (T < 1 || KV < 1 || H < KV || hd < 1 || max_keys < 1) return 0;  // an empty shape needs nothing (the call itself refuses it)
   return fb::attention_workspace(T * KV, H / KV, hd, max_keys, nullptr);
 }
 
@@ -370,7 +377,7 @@ extern "C" int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H
   fb::AttnArgs a{};
   a.q = (const uint16_t*)q, a.q_s0 = ld_q, a.q_s1 = (int64_t)rep * hd, a.q_sr = hd;  // entry (token, kv head): its rep query heads
   a.k = (const uint16_t*)cache, a.v = (const uint16_t*)cache + (int64_t)KV * cache_head_stride;
-  a.kv_s0 = 0, a.kv_s1 = cache_head_stride, a.base = base;
+  a.kv_s0 = 0, a.kv_s1 = cache_head_stride, a.base = base, a.kv_rows = cache_rows;
   a.place = place, a.p_s0 = 1, a.p_s1 = 0, a.p_sr = 0;
   a.E1 = KV, a.rows = rep, a.window = window, a.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   a.out = (uint16_t*)out, a.o_s0 = ld_o, a.o_s1 = (int64_t)rep * hd, a.o_sr = hd;
@@ -400,6 +407,7 @@ extern "C" int fb_decode_attention_packed(int cache_fmt, const void* q, int64_t 
 }
 
 extern "C" size_t fb_attend_workspace_bytes(int64_t entries, int64_t rows, int hd, int64_t max_keys) {
+  if (entries < 1 || rows < 1 || hd < 1 || max_keys < 1) return 0;
   return fb::attention_workspace(entries, (int)rows, hd, max_keys, nullptr);
 }
 
@@ -414,7 +422,7 @@ extern "C" int fb_attend(const void* q, int64_t entries, int64_t rows, int hd, i
              "fb_attend: rows 16-byte aligned");
   fb::AttnArgs a{};
   a.q = (const uint16_t*)q, a.q_s0 = q_entry_stride * kv_rep, a.q_s1 = q_entry_stride, a.q_sr = q_row_stride;
-  a.k = (const uint16_t*)k, a.v = (const uint16_t*)v, a.kv_s0 = kv_entry_stride, a.kv_s1 = 0, a.base = nullptr;  // kv_rep entries share a key matrix
+  a.k = (const uint16_t*)k, a.v = (const uint16_t*)v, a.kv_s0 = kv_entry_stride, a.kv_s1 = 0, a.base = nullptr, a.kv_rows = keys;  // kv_rep entries share a key matrix
   a.place = places, a.p_s0 = place_entry_stride * kv_rep, a.p_s1 = place_entry_stride, a.p_sr = place_row_stride;
   a.E1 = (int)kv_rep, a.rows = (int)rows, a.window = window, a.scale_log2 = 1.4426950408889634f * scale;
   a.out = (uint16_t*)out, a.o_s0 = rows * hd * kv_rep, a.o_s1 = rows * hd, a.o_sr = hd;
@@ -439,17 +447,26 @@ extern "C" size_t fb_decode_attention_static_max_bytes(void) { return fb::STATIC
 extern "C" int fb_decode_attention_static(const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
                                           int64_t cache_head_stride, const int32_t* base, const int32_t* place, int64_t max_keys, int window,
                                           void* out, int64_t ld_o, void* stream) {
-  FB_REQUIRE(KV >= 1 && H >= 1 && H % KV == 0, "fb_decode_attention_static: whole groups of query heads per key head");
+  FB_REQUIRE(T >= 1 && KV >= 1 && H >= 1 && H % KV == 0 && (hd == 64 || hd == 128) && max_keys >= 1,
+             "fb_decode_attention_static: at least one token, whole groups of query heads per key head, heads of 64 or 128 columns");
   const size_t need = fb_decode_attention_workspace_bytes(T, H, KV, hd, max_keys);
   FB_REQUIRE(need <= fb::STATIC_SCRATCH_BYTES,
              "fb_decode_attention_static: this call needs %zu bytes of scratch, the built-in array holds %zu: fewer tokens per call, or "
              "fb_decode_attention with a workspace of the caller's",
              need, fb::STATIC_SCRATCH_BYTES);
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fb::launch_status("fb_decode_attention_static (cudaGetDevice)");
+  if (cudaError_t e = cudaGetDevice(&dev)) {
+    fb::set_error("fb_decode_attention_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    return FB_ERR_LAUNCH;
+  }
+  FB_REQUIRE(dev >= 0 && dev < 64, "fb_decode_attention_static: device ordinal %d is beyond the 64 this entry point keeps an address for", dev);
   if (!fb::g_scratch_ptr[dev]) {  // set-up, on the first call on this device: in host code the array's name is not its device address
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, fb::g_attention_scratch) != cudaSuccess || !p) return fb::launch_status("fb_decode_attention_static (cudaGetSymbolAddress)");
+    const cudaError_t e = cudaGetSymbolAddress(&p, fb::g_attention_scratch);
+    if (e != cudaSuccess || !p) {
+      fb::set_error("fb_decode_attention_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return FB_ERR_LAUNCH;
+    }
     fb::g_scratch_ptr[dev] = p;
   }
   return fb_decode_attention(q, T, ld_q, H, KV, hd, cache, cache_rows, cache_head_stride, base, place, max_keys, window, out, ld_o,

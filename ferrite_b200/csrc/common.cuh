@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/ferrite_b200.h"
 
 namespace fb {
@@ -12,6 +14,9 @@ namespace fb {
 // fb_status and leaves the reason here (fb_last_error()).
 void set_error(const char* fmt, ...);
 int launch_status(const char* what);  // cudaGetLastError() -> FB_OK / FB_ERR_LAUNCH with the message kept
+// the status words of the kernels that wait (each reads and clears its own): 0, or the code of the wait that gave up
+int status_word_tcgen05();
+int status_word_peer();
 
 #define FB_REQUIRE(cond, ...)            \
   do {                                   \
@@ -20,6 +25,16 @@ int launch_status(const char* what);  // cudaGetLastError() -> FB_OK / FB_ERR_LA
       return FB_ERR_ARG;                 \
     }                                    \
   } while (0)
+
+// True the first time it is called on the current device for this mask: what is set up per device (a kernel's
+// shared-memory opt-in, a symbol's address) keeps one mask.  Two threads racing both see true at worst, which only
+// repeats the set-up.
+inline bool first_on_device(std::atomic<uint64_t>& seen) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+  const uint64_t bit = 1ull << dev;
+  return !(seen.fetch_or(bit) & bit);
+}
 
 __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

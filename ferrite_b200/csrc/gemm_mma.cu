@@ -352,11 +352,8 @@ template <int FMT, int NT>
 int launch_mma(MmaParams p, int64_t blocks, cudaStream_t s) {
   auto kernel = linear_mma_kernel<FMT, NT>;
   const size_t smem = mma_smem_bytes(FMT, NT);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> opted{0};  // the shared-memory opt-in, once per device
+  if (first_on_device(opted)) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   cudaLaunchConfig_t cfg{};
   cfg.blockDim = dim3(MTHREADS), cfg.dynamicSmemBytes = smem, cfg.stream = s;
   cudaLaunchAttribute attr[2];

@@ -614,9 +614,4 @@ int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStrea
 
 }  // namespace fb
 
-extern "C" int fb_status_word(void) {
-  int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, fb::g_status_word, sizeof v) != cudaSuccess) return FB_ERR_LAUNCH;
-  if (v) cudaMemcpyToSymbol(fb::g_status_word, &zero, sizeof zero);
-  return v;
-}
+int fb::status_word_tcgen05() { return fb::read_and_clear_status_word(); }

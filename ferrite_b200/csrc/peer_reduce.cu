@@ -7,7 +7,8 @@
 //   1. tells every rank (a release store at system scope into that rank's flag word for it) that its partial of call
 //      number e is in place - it was written by the kernel before this one in the stream, into memory every rank maps;
 //   2. waits until every rank has told it so (acquire loads of its own flag words, bounded: a rank that never arrives
-//      costs ~2 s, leaves 201 + its number in state[2], and the call returns with what is there);
+//      costs ~2 s - or state[3] clock cycles, when that is not 0 -, leaves 201 + its number in state[2] and in the
+//      library's status word (fb_status_word), and the call returns with what is there);
 //   3. adds the partials in rank order 0, 1, ... in fp32 - the same order on every rank, so all ranks hold bit-identical
 //      results and stay in step - adds the residual, rounds once to bf16.
 // The call number lives on the device (state[0]) and is advanced by the last CTA to finish, so a recorded graph can
@@ -26,7 +27,7 @@ struct PeerArgs {
   const uint16_t* partial[MAX_RANKS];  // each rank's partial of this call site (peer-mapped addresses), bf16 [count]
   uint32_t* flags[MAX_RANKS];          // each rank's flag words: flags[r][s] = the last call rank s has entered
   uint32_t* state;                     // this rank's: [0] calls completed, [1] CTAs of the running call that are done,
-                                       // [2] 0, or 201 + the rank a wait gave up on
+                                       // [2] 0, or 201 + the rank a wait gave up on, [3] the wait's bound in clocks (0: WAIT_CLOCKS)
   const uint16_t* residual;            // bf16 [count] or null
   uint16_t* out;                       // bf16 [count]
   int64_t count;
@@ -66,11 +67,13 @@ __global__ void __launch_bounds__(256) peer_reduce_add_kernel(const PeerArgs a) 
   // (after a wait has given up once, later calls do not wait again: the caller finds the code in state[2] within seconds)
   if (threadIdx.x < a.world && *reinterpret_cast<volatile uint32_t*>(a.state + 2) == 0) {  // one thread per rank waited for
     const uint32_t* flag = a.flags[a.rank] + threadIdx.x;
-    const long long start = clock64();
+    const uint32_t own = *reinterpret_cast<volatile uint32_t*>(a.state + 3);
+    const long long limit = own ? (long long)own : WAIT_CLOCKS, start = clock64();
     // (flags only grow; the difference is taken modulo 2^32 so that the count may wrap)
     while ((int32_t)(load_acquire_sys(flag) - e) < 0) {
-      if (clock64() - start > WAIT_CLOCKS) {
+      if (clock64() - start > limit) {
         atomicCAS(a.state + 2, 0u, (uint32_t)WAIT_PEER + threadIdx.x);  // (the caller reads and clears it)
+        atomicCAS(&g_status_word, 0, (int)WAIT_PEER + (int)threadIdx.x);
         break;
       }
       __nanosleep(64);
@@ -117,6 +120,8 @@ __global__ void __launch_bounds__(256) peer_reduce_add_kernel(const PeerArgs a) 
 }
 
 }  // namespace
+
+int status_word_peer() { return read_and_clear_status_word(); }
 
 }  // namespace fb
 

@@ -9,6 +9,15 @@ namespace fb {
 static __device__ int g_status_word = 0;
 constexpr long long WAIT_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz: no healthy wait comes near it
 
+// host: this translation unit's status word, read and cleared (synchronises with the device); fb_status_word() asks
+// every translation unit whose kernels wait
+static inline int read_and_clear_status_word() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_status_word, sizeof v) != cudaSuccess) return FB_ERR_LAUNCH;
+  if (v) cudaMemcpyToSymbol(g_status_word, &zero, sizeof zero);
+  return v;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -154,10 +154,12 @@ def added(x, y, c):
 def tensor_parallel(c, rank, world, group=None):
     """c as rank `rank` of `world` holds it: its share of the query and key heads, of the MLP's columns and of the
     vocabulary (models too large or too slow for one GPU; the reference has no counterpart: one chip, ferrite/runtime.py:304-311)."""
-    assert c.heads % world == 0 and c.kv % world == 0 and (c.ffn or 0) % world == 0 and c.vocab % (16 * world) == 0, "shards of whole heads and runs"
+    assert c.heads % world == 0 and (c.ffn or 0) % world == 0 and c.vocab % (16 * world) == 0, "shards of whole heads and runs"
+    # fewer key heads than ranks: each key head (and its values) is kept by world / kv ranks, which share out its query heads
+    assert c.kv % world == 0 or (world % c.kv == 0 and (c.heads // c.kv) % (world // c.kv) == 0), "whole key heads, or whole shares of one key head's queries"
     assert (getattr(c, "experts", 0) or 0) % world == 0, "every rank holds the same number of whole experts"
     local = SimpleNamespace(**vars(c))
-    local.head_dim, local.heads, local.kv, local.dim = head(c), c.heads // world, c.kv // world, c.dim
+    local.head_dim, local.heads, local.kv, local.dim = head(c), c.heads // world, max(c.kv // world, 1), c.dim
     local.ffn, local.vocab_shard = (c.ffn or 0) // world, c.vocab // world
     local.tp = SimpleNamespace(rank=rank, world=world, group=group, peer=None)
     return local
@@ -182,6 +184,10 @@ def tp_keep(name, full, rank, world):
     run = lambda first, size: np.arange(first + rank * (size // world), first + (rank + 1) * (size // world))
     op = name.split(".")[-1]
     if op == "qkv_proj":
+        if KV % world:  # fewer key heads than ranks: the one key head this rank's query heads belong to, and its values
+            mine = rank * KV // world
+            one = lambda first: np.arange(first + mine * hd, first + (mine + 1) * hd)
+            return 1, np.concatenate([run(0, H * hd), one(H * hd), one((H + KV) * hd)])
         return 1, np.concatenate([run(0, H * hd), run(H * hd, KV * hd), run((H + KV) * hd, KV * hd)])
     if op == "o_proj":
         return 0, run(0, H * hd)

@@ -72,18 +72,25 @@ def unpack_fields(p):
 
 
 _WORKSPACES = {}
+_RETIRED = []  # scratch buffers a larger one has replaced: a recorded CUDA graph may still hold their addresses
+
+
+def _scratch(table, device, nbytes, least):
+    """The device's buffer of one kind of scratch: zeroed when made, replaced by a larger one when a call needs more.
+    The one it replaces is kept alive for good: a step recorded by `jit` replays kernels that were given its address."""
+    have = table.get(device)
+    if have is None or have.numel() < nbytes:
+        if have is not None:
+            _RETIRED.append(have)
+        have = table[device] = torch.zeros(max(nbytes, least), dtype=torch.uint8, device=device)
+    return have
 
 
 def linear_workspace(device, nbytes):
-    """The device's scratch buffer for fb_linear (split-K partial tiles, tile counters, the normalised
-    activations): one per device, zeroed when made (the counters start at 0 and every call leaves them 0),
-    grown when a call needs more.  Calls on one stream run in order, so they can share it."""
-    if not nbytes:
-        return None
-    have = _WORKSPACES.get(device)
-    if have is None or have.numel() < nbytes:
-        have = _WORKSPACES[device] = torch.zeros(max(nbytes, 64 << 20), dtype=torch.uint8, device=device)
-    return have
+    """The device's scratch buffer for fb_linear (the normalised activations of a fused RMSNorm, the partial tiles and
+    arrival counters of tiles shared by several CTAs): one per device, zeroed when made (the counters start at 0 and
+    every call leaves them 0).  Calls on one stream run in order, so they can share it."""
+    return _scratch(_WORKSPACES, device, nbytes, 64 << 20) if nbytes else None
 
 
 def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="none", residual=None, workspace=None):
@@ -126,7 +133,7 @@ def rope_kv_write(qkv, cos, sin, places, rows, cache, H, KV, hd, q_out=None, qk_
         if q_out is None:
             q_out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=qkv.device)
         check(lib().fb_rope_kv_write_packed(cache.code, qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1],
-                                            places.data_ptr(), rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0),
+                                            cos.shape[0], places.data_ptr(), rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0),
                                             cache.data.data_ptr(), cache.K, _stream()))
         count()
         return q_out
@@ -135,7 +142,7 @@ def rope_kv_write(qkv, cos, sin, places, rows, cache, H, KV, hd, q_out=None, qk_
     assert cos.shape == sin.shape and cos.is_contiguous() and sin.is_contiguous() and cos.dtype == torch.bfloat16
     if q_out is None:
         q_out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=qkv.device)
-    check(lib().fb_rope_kv_write(qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1], places.data_ptr(),
+    check(lib().fb_rope_kv_write(qkv.data_ptr(), T, qkv.stride(0), H, KV, hd, cos.data_ptr(), sin.data_ptr(), cos.shape[-1], cos.shape[0], places.data_ptr(),
                                  rows.data_ptr(), _ptr(qk_norm), eps, q_out.data_ptr(), q_out.stride(0), cache.data_ptr(), cache.shape[1], cache.stride(0), _stream()))
     count()
     return q_out
@@ -154,9 +161,7 @@ def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=N
     if out is None:
         out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=q.device)
     need = lib().fb_decode_attention_workspace_bytes(T, H, KV, hd, max_keys)
-    ws = _ATT_WS.get(q.device)
-    if need and (ws is None or ws.numel() < need):
-        ws = _ATT_WS[q.device] = torch.empty(need, dtype=torch.uint8, device=q.device)
+    ws = attention_workspace(q.device, need)
     if packed:
         check(lib().fb_decode_attention_packed(cache.code, q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data.data_ptr(), cache.K, base.data_ptr(),
                                                place.data_ptr(), max_keys, window, out.data_ptr(), out.stride(0), _ptr(ws) if need else None,
@@ -189,13 +194,9 @@ def argmax(logits, out=None, values=None):
 
 
 def attention_workspace(device, nbytes):
-    """The device's scratch for the attention kernels' key splits (grown when a call needs more)."""
-    if not nbytes:
-        return None
-    ws = _ATT_WS.get(device)
-    if ws is None or ws.numel() < nbytes:
-        ws = _ATT_WS[device] = torch.empty(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
-    return ws
+    """The device's scratch for the attention kernels' key splits (a larger one replaces it when a call needs more;
+    the replaced one stays alive for the recorded steps that hold its address)."""
+    return _scratch(_ATT_WS, device, nbytes, 16 << 20) if nbytes else None
 
 
 def linear_indexed(x, w, index, out, sum_slots=False, x_slot_rows=0, out_slot_stride=0, M=None, out_dtype="bf16", norm_w=None, eps=1e-5,

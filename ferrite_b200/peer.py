@@ -21,6 +21,7 @@ class PeerReduce:
     def __init__(self, rt, group, count, sites):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
+        assert sites >= 2, "two staging buffers at least: a rank may refill one while another still reads the call before's"
         self.rt, self.group, self.count, self.sites = rt, group, count, sites
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         nbytes = FLAG_BYTES + sites * count * 2
@@ -54,7 +55,9 @@ class PeerReduce:
         n = min(self.count, 4096)
         out = torch.empty(n, dtype=torch.bfloat16, device=self.rt.device)
         for i in range(3):
-            self.new_step()
+            # (sites in turn: a rank leaves call i once every rank has entered it, not finished reading - it must not
+            # refill the buffer a slower rank is still adding up)
+            self.next_site = i % 2
             self.stage(1, n).fill_(float(self.rank + 1 + i))
             self.reduce_add(n, None, out)
             torch.cuda.synchronize(self.rt.device)

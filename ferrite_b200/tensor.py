@@ -366,10 +366,7 @@ class Tensor:
         t, ids = self.realize(), ids.realize()
         table = t.buf[0] if t.buf[0].is_contiguous() else t.buf[0].contiguous()
         out = Tensor(self.rt, ids.cols, self.cols, dtype=self.dtype)
-        if (self.cols * table.element_size()) % 16 == 0:
-            ops.gather_rows(table, ids.buf.reshape(-1), out.buf[0])
-        else:  # rows that are not whole 16-byte pieces: one row at a time through the copy kernel's strides
-            _gather_slow(table, ids, out)
+        ops.gather_rows(table, ids.buf.reshape(-1), out.buf[0])
         self.rt.launched("gather")
         return out
 
@@ -410,7 +407,7 @@ class Tensor:
         each row's last key; with a window, only the last `window` keys.  bf16 keys and values."""
         rep = k.args.get("n", 1) if k.op == "repeat" else 1
         assert (v.args.get("n", 1) if v.op == "repeat" else 1) == rep and self.batch == k.batch == v.batch
-        assert self.dtype == "bf16" and k.dtype == v.dtype == "bf16", "bf16 queries, keys and values (a block-float cache is not built yet)"
+        assert self.dtype == "bf16" and k.dtype == v.dtype == "bf16", "bf16 queries, keys and values (a block-float cache is read by attend_cache)"
         assert self.cols == k.cols == v.cols and self.cols in (64, 128) and k.rows == v.rows, "heads of 64 or 128 columns"
         assert places.rows == self.rows and places.batch in (1, self.batch) and places.cols == 1 and places.dtype == "int32", \
             f"{self.shape} by {k.shape}, {places.shape}"
@@ -860,10 +857,6 @@ def _copy(src, dst):
 
 def _fill(t, value):
     _run_elementwise(t._lazy("add", (value, 0), t.shape, t.dtype), into=t)
-
-
-def _gather_slow(table, ids, out):
-    raise AssertionError("gather: rows of whole 16-byte pieces")
 
 
 def jit(f):

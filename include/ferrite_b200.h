@@ -133,7 +133,8 @@ int fb_linear_indexed(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx,
 /* ---- the rest of a decode step ------------------------------------------------------------------------- */
 
 /* out[i, :] = table[ids[i], :]: Tensor.gather, the embedding lookup (ferrite/tensor.py:116-126,
- * ferrite/compiler.py:1574-1580).  ids are read on the device; rows of row_bytes bytes (a multiple of 16). */
+ * ferrite/compiler.py:1574-1580).  ids are read on the device (an id outside the table is clamped into it); rows of
+ * row_bytes bytes (even; whole 16-byte pieces at 16-byte aligned addresses go 16 bytes at a time). */
 int fb_gather_rows(const void* table, int64_t table_rows, int64_t row_bytes, const int32_t* ids, int64_t n, void* out,
                    void* stream);
 
@@ -148,11 +149,13 @@ int fb_put_rows(void* dst, int64_t ds0, int64_t ds1, int64_t ds2, const void* sr
  * (Tensor.put, ferrite/tensor.py:128-140; ferrite/compiler.py:1638-1650): cache[(k heads, v heads)][rows[t]][:],
  * cache laid out [2*KV, cache_rows, hd] as models/llama.py:506-514.  cos / sin: [places, table_cols] with
  * table_cols = hd (one head's table) or (H + 2*KV)*hd (ferrite's, v's columns 1 and 0).  places[t] picks the
- * table row, rows[t] the cache row (place + the sequence's first row, llama.py:443-445).  cache_head_stride: elements
+ * table row (clamped into the table's table_rows rows), rows[t] the cache row (place + the sequence's first row,
+ * llama.py:443-445; a row outside 0 .. cache_rows-1 is not written: ferrite checks neither, nothing here reads or
+ * writes outside what it was given).  cache_head_stride: elements
  * from one head's rows to the next's (cache_rows * hd, or more when the cache is one sequence's part of a larger one,
  * models/llama.py:520-526). */
 int fb_rope_kv_write(const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos, const void* sin,
-                     int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps,
+                     int64_t table_cols, int64_t table_rows, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps,
                      void* q_out, int64_t ld_q, void* cache, int64_t cache_rows, int64_t cache_head_stride, void* stream);
 
 /* softmax(q k^T / sqrt(hd) + mask) v over the bf16 KV cache for one token per sequence: Tensor.attend
@@ -173,7 +176,7 @@ int fb_decode_attention(const void* q, int64_t T, int64_t ld_q, int H, int KV, i
  * same bf16 values a bf16 cache would hold and then computes what fb_decode_attention computes, bit for bit.
  * base[t] (a sequence's first cache row) must be a multiple of 64: a sequence's rows start a packed unit. */
 int fb_rope_kv_write_packed(int cache_fmt, const void* qkv, int64_t T, int64_t ld_qkv, int H, int KV, int hd, const void* cos, const void* sin,
-                            int64_t table_cols, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps, void* q_out,
+                            int64_t table_cols, int64_t table_rows, const int32_t* places, const int32_t* rows, const void* qk_norm, float eps, void* q_out,
                             int64_t ld_q, void* cache_packed, int64_t cache_rows, void* stream);
 int fb_decode_attention_packed(int cache_fmt, const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache_packed,
                                int64_t cache_rows, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out,
@@ -259,8 +262,9 @@ int fb_matmul(const void* a, const int64_t* a_strides_host, int a_dtype, const v
  * partials[r], flags[r]: HOST arrays of `world` device addresses, valid on this GPU, of rank r's partial for this call
  * site and of rank r's flag words (`world` uint32, zero before the first call); every rank passes the same buffers in
  * the same order and makes the same sequence of calls.  state: 4 uint32 of this GPU, zero before the first call
- * ([0] counts the calls; [2] holds 201 + r after a bounded wait for rank r gave up, else 0).  The partial of a call
- * site may be overwritten as soon as a later call has been launched behind this one.  count: a multiple of 8.
+ * ([0] counts the calls; [2] holds 201 + r after a bounded wait for rank r gave up, else 0; [3]: the wait's bound in
+ * clock cycles, 0 for the default of about two seconds).  The partial of a call site may be overwritten once a later
+ * call has passed its wait (every rank has then finished reading it).  count: a multiple of 8.
  * All ranks add in rank order, so their results are bit-identical. */
 int fb_peer_reduce_add(const void* const* partials, void* const* flags, int rank, int world, void* state, int64_t count,
                        const void* residual, void* out, void* stream);

@@ -204,15 +204,45 @@ def experts(h, p, ids, w):
     return np.stack(rows)
 
 
-def moe(h, p, c, live=None):
-    """Router logits -> top-k -> softmax weights -> weighted experts (models/llama.py:277-292)."""
+def experts_by_expert(h, p, ids, w):
+    """experts(), with each expert's matrices multiplied once by all the tokens that pick it instead of once per token
+    and pick (the same terms, added per token in the same order): for mixtures whose experts are too large to widen to
+    float64 a hundred times over.  tests/test_oracle.py holds it equal to experts()."""
+    gu, down = p["experts.gate_up"], p["experts.down"]
+    m = down.shape[-2]
+    terms = {}
+    for e in sorted({int(v) for v in ids.ravel()}):
+        rows = [t for t in range(len(h)) if e in ids[t]]
+        g = h[rows] @ gu[e]
+        y = glu(g[:, :m], g[:, m:]) @ down[e]
+        terms |= {(t, e): y[i] for i, t in enumerate(rows)}
+    out = []
+    for t in range(len(h)):
+        acc = w[t, 0] * terms[t, int(ids[t, 0])]
+        for j in range(1, ids.shape[1]):
+            acc = acc + w[t, j] * terms[t, int(ids[t, j])]
+        out.append(acc)
+    return np.stack(out)
+
+
+def moe(h, p, c, live=None, picks=None):
+    """Router logits -> top-k -> softmax weights -> weighted experts (models/llama.py:277-292).
+    picks (not in the reference): expert ids [tokens, k] to use instead of this function's own top-k, their weights
+    still computed here from this function's logits - a test feeds the device's picks so that a near tie between the
+    k-th and the next logit, which a bf16 rounding of the hidden state can turn, does not send the two down different
+    experts (the reference's own test picks prompts without such ties instead, test/test_sim.py:1550-1552)."""
     logits = h @ p["router"]
-    if c.norm_topk:
+    if picks is not None:
+        ids = np.asarray(picks)
+        chosen = np.take_along_axis(logits if c.norm_topk else softmax(logits), ids, -1)
+        w = softmax(chosen) if c.norm_topk else chosen
+    elif c.norm_topk:
         vals, ids = topk(logits, c.k)
         w = softmax(vals)
     else:
         w, ids = topk(softmax(logits), c.k)
-    return experts(h, p, ids, w if live is None else w * live)
+    run = experts_by_expert if getattr(c, "by_expert", False) else experts
+    return run(h, p, ids, w if live is None else w * live)
 
 
 def touched(ids, weights, n):
@@ -236,11 +266,11 @@ def block(w, prefix):
     return {k[len(prefix):]: v for k, v in w.items() if k.startswith(prefix)}
 
 
-def layer(x, p, c, cos, sin, mask, cache, rows, live=None, slots=None):
+def layer(x, p, c, cos, sin, mask, cache, rows, live=None, slots=None, picks=None):
     """Attention then MLP (or MoE), each after an RMSNorm and added back (models/llama.py:95-109)."""
     x = x + attention(rms(x, p["input_layernorm"], c.eps), p, c, cos, sin, mask, cache, rows, slots)
     h = rms(x, p["post_attention_layernorm"], c.eps)
-    return x + (moe(h, p, c, live) if "router" in p else mlp(h, p))
+    return x + (moe(h, p, c, live, picks) if "router" in p else mlp(h, p))
 
 
 def around(w, c, places, size, slots=None):
@@ -260,14 +290,14 @@ def around(w, c, places, size, slots=None):
     return rows, cos, sin, key_mask(column, part), live
 
 
-def forward(ids, places, w, c, caches, slots=None, every=False):
+def forward(ids, places, w, c, caches, slots=None, every=False, picks=None):
     """Logits for the token after `ids` at `places` (models/llama.py:459-480): the last token's, or every
-    token's with slots / every."""
+    token's with slots / every.  picks: per block, the experts to use (see moe), or None."""
     x = w["embed"][list(ids)]
     size = caches[0].shape[-2]
     rows, cos, sin, mask, live = around(w, c, places, size, slots)
     for l in range(c.layers):
-        x = layer(x, block(w, f"layers.{l}."), c, cos, sin, mask, caches[l], rows, live, slots)
+        x = layer(x, block(w, f"layers.{l}."), c, cos, sin, mask, caches[l], rows, live, slots, picks[l] if picks else None)
     h = rms(x, w["norm"], c.eps)
     return (h if slots or every else h[-1:]) @ w["embed.T"]
 

@@ -50,9 +50,19 @@ def test_new_entry_points_refuse_bad_arguments_without_a_gpu():
     assert rc == -1 and b"up to 8 ranks" in lib.fb_last_error()
     rc = lib.fb_peer_reduce_add(two, two, 0, 2, 16, 60, None, 16, None)
     assert rc == -1 and b"16-byte pieces" in lib.fb_last_error()
-    rc = lib.fb_rope_kv_write_packed(_lib.BF16, 16, 1, 256, 2, 1, 64, 16, 16, 64, 16, 16, None, 1e-5, 16, 128, 16, 64, None)
+    rc = lib.fb_rope_kv_write_packed(_lib.BF16, 16, 1, 256, 2, 1, 64, 16, 16, 64, 8, 16, 16, None, 1e-5, 16, 128, 16, 64, None)
     assert rc == -1 and b"bfp8 or bfp4 cache" in lib.fb_last_error()
     rc = lib.fb_decode_attention_packed(_lib.BFP8, 16, 1, 128, 2, 1, 96, 16, 64, 16, 16, 64, 0, 16, 128, None, 0, None)
     assert rc == -1 and b"64 or 128" in lib.fb_last_error()
     rc = lib.fb_touched(16, 16, 4, 40, 8, 0, 16, 16, None)
     assert rc == -1 and b"up to 32 choices" in lib.fb_last_error()
+
+
+def test_empty_shapes_need_no_workspace_and_static_attention_refuses_them():
+    lib = _lib.lib()
+    assert lib.fb_decode_attention_workspace_bytes(0, 8, 2, 128, 64) == 0 and lib.fb_decode_attention_workspace_bytes(4, 8, 0, 128, 64) == 0
+    assert lib.fb_attend_workspace_bytes(0, 4, 128, 64) == 0
+    rc = lib.fb_decode_attention_static(16, 0, 1024, 8, 2, 128, 16, 64, 8192, 16, 16, 64, 0, 16, 1024, None)
+    assert rc == -1 and b"at least one token" in lib.fb_last_error()
+    rc = lib.fb_rope_kv_write(16, 1, 256, 2, 1, 48, 16, 16, 48, 8, 16, 16, 16, 1e-5, 16, 96, 16, 64, 64 * 48, None)
+    assert rc == -1 and b"multiple of 64" in lib.fb_last_error()

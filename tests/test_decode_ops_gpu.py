@@ -92,3 +92,65 @@ def test_attention_misuse_is_refused(cuda):
     z = torch.zeros(1, dtype=torch.int32, device=cuda)
     with pytest.raises(AssertionError):
         ops.decode_attention(q, cache, z, z, 1, 1, 96, max_keys=32)  # heads are 64 or 128 wide
+
+
+def test_rows_and_places_outside_the_cache_touch_nothing(cuda):
+    # a cache row past the cache (decoding beyond a sequence's part) is not written, a place past the RoPE tables reads
+    # the tables' last row, and attention reads no key past the cache whatever a place says: the cache sits inside a
+    # larger buffer of a known pattern, which must come back unchanged, and attention equals the clamped oracle
+    H, KV, hd, size = 4, 2, 64, 64
+    rng = np.random.default_rng(9)
+    c = llama.model(dim=H * hd, heads=H, kv=KV, head_dim=hd, layers=1, eps=1e-6, theta=10000.0)
+    cos, sin = llama.rotary(c, size)
+    guard = 4096
+    buf = torch.full((guard + 2 * KV * size * hd + guard,), 7.0, dtype=torch.bfloat16, device=cuda)
+    cache = buf[guard:guard + 2 * KV * size * hd].view(2 * KV, size, hd)
+    cache.zero_()
+    qkv = bfp.bf16_round(rng.normal(0, 1, (3, (H + 2 * KV) * hd)).astype(np.float32))
+    places = torch.tensor([5, size + 40, -3], dtype=torch.int32, device=cuda)      # one inside the tables, two outside
+    rows = torch.tensor([5, size, -1], dtype=torch.int32, device=cuda)             # one inside the cache, two outside
+    ops.rope_kv_write(to_bf16_tensor(qkv, cuda), to_bf16_tensor(cos[:, :hd], cuda).contiguous(), to_bf16_tensor(sin[:, :hd], cuda).contiguous(),
+                      places, rows, cache, H, KV, hd)
+    torch.cuda.synchronize()
+    assert bool((buf[:guard] == 7.0).all()) and bool((buf[-guard:] == 7.0).all()), "nothing outside the cache is written"
+    written = to_numpy(cache).any(-1)
+    assert written[:, 5].all() and written.sum() == 2 * KV, "only the row inside the cache is written"
+    # attention: a place of 10 * size sees the whole cache and nothing more
+    cache.copy_(to_bf16_tensor(bfp.bf16_round(rng.normal(0, 1, (2 * KV, size, hd)).astype(np.float32)), cuda))
+    q = bfp.bf16_round(rng.normal(0, 1, (2, H * hd)).astype(np.float32))
+    base = torch.tensor([0, 32], dtype=torch.int32, device=cuda)
+    far = torch.tensor([10 * size, 10 * size], dtype=torch.int32, device=cuda)
+    got = to_numpy(ops.decode_attention(to_bf16_tensor(q, cuda), cache, base, far, H, KV, hd, max_keys=size))
+    want = attention_oracle(q.astype(np.float64), to_numpy(cache), [0, 32], [size - 1, size - 33], H, KV, hd)
+    assert np.abs(got - want).max() < 0.01 * np.abs(want).max() + 1e-3
+
+
+def test_a_recorded_step_survives_a_larger_workspace(cuda):
+    # a step recorded as a CUDA graph holds the address of the attention scratch it was given; a later, larger call
+    # replaces that scratch, and the recorded step must still compute what it computed (the replaced buffer stays alive)
+    H, KV, hd, size, T = 8, 2, 128, 1024, 4
+    gen = torch.Generator(device=cuda).manual_seed(2)
+    cache = torch.empty(2 * KV, T * size, hd, dtype=torch.bfloat16, device=cuda).normal_(0, 1, generator=gen)
+    q = torch.empty(T, H * hd, dtype=torch.bfloat16, device=cuda).normal_(0, 1, generator=gen)
+    base = torch.arange(T, dtype=torch.int32, device=cuda) * size
+    place = torch.full((T,), size - 1, dtype=torch.int32, device=cuda)
+    out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=cuda)
+    ops._ATT_WS.pop(cuda, None)  # start from no scratch, so that the recorded call's is small
+    ops.decode_attention(q, cache, base, place, H, KV, hd, size, out=out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.decode_attention(q, cache, base, place, H, KV, hd, size, out=out)
+    graph.replay()
+    torch.cuda.synchronize()
+    want = out.clone()
+    held = ops._ATT_WS[cuda]
+    # a much larger call: more tokens, so more partial sums than the recorded call's scratch holds
+    T2 = 512
+    big = ops.attention_workspace(cuda, held.numel() * 4)
+    assert big is not held and any(r is held for r in ops._RETIRED), "the replaced scratch is kept"
+    fill = torch.empty(64 << 20, dtype=torch.uint8, device=cuda).fill_(255)  # memory a freed scratch would have been handed out as
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want) and int(fill[0]) == 255

@@ -158,3 +158,14 @@ def test_chunked_prefill_matches_reference_vectors():
     for tokens in (1, 4, 13):
         got = llama.prefill(g["ids"].tolist(), w, c, llama.kv_cache(c, 32), tokens)
         assert np.allclose(got[0], g[f"logits{tokens}"], rtol=1e-9, atol=1e-9), tokens
+
+
+def test_experts_by_expert_is_experts():
+    # the grouped evaluation the large-shape GPU tests use gives what the reference's per-token loop gives
+    g = golden("moe.npz")
+    w = {k: bfp.bf16_floats(g[k]) for k in ("router", "experts.gate_up", "experts.down")}
+    c = llama.model(dim=64, k=4)
+    h = bfp.bf16_floats(g["h40"]).astype(np.float64)
+    want = llama.moe(h, w, c)
+    c.by_expert = True
+    assert np.allclose(llama.moe(h, w, c), want, rtol=1e-10, atol=1e-12)

@@ -116,3 +116,29 @@ def test_two_ranks_reproduce_one_device():
         p.join(120)
         assert p.exitcode == 0
     assert result.get(timeout=5) is True
+
+
+def test_key_heads_shared_by_ranks_when_there_are_fewer_of_them():
+    # eight ranks on four key heads: ranks 2j and 2j + 1 both keep key head j (and its values) and share out its query
+    # heads; every rank's attention over its own heads, through its rows of o_proj, sums to the whole block's
+    from ferrite_b200 import llama
+    full = llama.model(dim=64, heads=16, kv=4, layers=1, vocab=1024, ffn=64, eps=1e-5, theta=10000.0)
+    hd, world = llama.head(full), 8
+    rng = np.random.default_rng(1)
+    wqkv, wo, x = rng.normal(0, 0.1, (64, (16 + 8) * hd)), rng.normal(0, 0.1, (16 * hd, 64)), rng.normal(0, 1, (3, 64))
+
+    def heads_out(qkv, H, KV):  # every query head's softmax(q k^T) v over the call's own tokens, side by side
+        q, k, v = (ollama.split_heads(qkv[:, a * hd:b * hd], b - a) for a, b in ((0, H), (H, H + KV), (H + KV, H + 2 * KV)))
+        k, v = np.repeat(k, H // KV, 0), np.repeat(v, H // KV, 0)
+        return ollama.merge_heads(ollama.softmax(q @ k.swapaxes(-1, -2)) @ v)
+
+    want = heads_out(x @ wqkv, 16, 4) @ wo
+    total = 0
+    for rank in range(world):
+        local = llama.tensor_parallel(full, rank, world)
+        assert (local.heads, local.kv) == (2, 1)
+        cols = llama.tp_keep("qkv_proj", full, rank, world)[1]
+        assert cols[2 * hd:3 * hd].tolist() == list(range((16 + rank // 2) * hd, (16 + rank // 2 + 1) * hd))
+        rows = llama.tp_keep("o_proj", full, rank, world)[1]
+        total = total + heads_out(x @ wqkv[:, cols], 2, 1) @ wo[rows]
+    assert np.allclose(total, want, rtol=1e-10, atol=1e-12)

@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libferrite_b200.so")
 BF16, FP32, INT32, BFP8, BFP4 = 0, 1, 2, 3, 4
 DTYPES = {"bf16": BF16, "fp32": FP32, "int32": INT32, "bfp8": BFP8, "bfp4": BFP4}
 EPI_NONE, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 2
-LINEAR_AUTO, LINEAR_TCGEN05, LINEAR_GEMV, LINEAR_MMA = 0, 1, 2, 3  # fb_linear_prefer
+LINEAR_AUTO, LINEAR_TCGEN05, LINEAR_GEMV, LINEAR_MMA, LINEAR_PERSISTENT = 0, 1, 2, 3, 4  # fb_linear_prefer
 
 _p, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 
@@ -36,10 +36,13 @@ SIGNATURES = {
     "fb_decode_attention": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _i64, _i64, _p, _p, _i64, _i, _p, _i64, _p, _sz, _p]),
     "fb_decode_attention_static_max_bytes": (_sz, []),
     "fb_decode_attention_static": (_i, [_p, _i64, _i64, _i, _i, _i, _p, _i64, _i64, _p, _p, _i64, _i, _p, _i64, _p]),
+    "fb_prefill_attention_workspace_bytes": (_sz, [_i64, _i, _i, _i64]),
+    "fb_prefill_attention": (_i, [_i, _p, _i64, _i64, _i, _i, _i, _p, _i64, _i64, _i64, _p, _i64, _i, _p, _i64, _p, _sz, _p]),
     "fb_attend_workspace_bytes": (_sz, [_i64, _i64, _i, _i64]),
     "fb_attend": (_i, [_p, _i64, _i64, _i, _i64, _i64, _p, _p, _i64, _i64, _i64, _p, _i64, _i64, _i, _f, _p, _p, _sz, _p]),
     "fb_topk": (_i, [_i, _p, _i64, _i64, _i64, _i, _p, _p, _p, _p, _i64, _p]),
     "fb_touched": (_i, [_p, _p, _i64, _i, _i, _i, _p, _p, _p]),
+    "fb_group": (_i, [_p, _i64, _i, _i, _p, _p, _p, _p]),
     "fb_elementwise": (_i, [_i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _p]),
     "fb_reduce": (_i, [_i, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _i, _p]),
     "fb_matmul": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),

@@ -31,6 +31,7 @@ struct AttnArgs {
   const uint16_t *k, *v;  // key j of entry e at k + e0*kv_s0 + e1*kv_s1 + (base[e0] + j)*hd
   int64_t kv_s0, kv_s1;
   const int32_t* base;   // [E0] first cache row of a sequence, or null
+  int64_t row0;          // added to it (a chunk of one sequence: its first cache row, with no base)
   const int32_t* place;  // row r of entry e sees keys 0..place[e0*p_s0 + e1*p_s1 + r*p_sr]
   int64_t p_s0, p_s1, p_sr;
   int E1, rows;  // rows per entry
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(AttnArgs 
     len = max(len, p + 1), least = min(least, p);
   }
   // a place past its sequence's rows (or a first row outside the cache) reads no key that is not there
-  const int64_t seq_first = a.base ? a.base[e0] : 0;
+  const int64_t seq_first = (a.base ? a.base[e0] : 0) + a.row0;
   const int64_t room = seq_first < 0 ? 0 : a.kv_rows - seq_first;
   len = (int)max((int64_t)0, min((int64_t)len, room));
   int first = a.window > 0 ? max(0, least + 1 - a.window) : 0;
@@ -427,6 +428,43 @@ extern "C" int fb_attend(const void* q, int64_t entries, int64_t rows, int hd, i
   a.E1 = (int)kv_rep, a.rows = (int)rows, a.window = window, a.scale_log2 = 1.4426950408889634f * scale;
   a.out = (uint16_t*)out, a.o_s0 = rows * hd * kv_rep, a.o_s1 = rows * hd, a.o_sr = hd;
   return fb::launch_attention(a, entries, hd, keys, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+// A chunk of ONE sequence's prompt: T tokens at places[t] (rising or not), each seeing the sequence's keys up to its own
+// place.  An entry is a query head over all the chunk's tokens, 16 tokens a CTA, so a key row is read once per 16
+// prompt tokens of a head instead of once per token (what the decode form would cost).
+extern "C" size_t fb_prefill_attention_workspace_bytes(int64_t T, int H, int hd, int64_t max_keys) {
+  if (T < 1 || H < 1 || hd < 1 || max_keys < 1) return 0;
+  return fb::attention_workspace(H, (int)T, hd, max_keys, nullptr);
+}
+
+extern "C" int fb_prefill_attention(int cache_fmt, const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache,
+                                    int64_t cache_rows, int64_t cache_head_stride, int64_t first_row, const int32_t* places, int64_t max_keys,
+                                    int window, void* out, int64_t ld_o, void* workspace, size_t workspace_bytes, void* stream) {
+  FB_REQUIRE(cache_fmt == 0 || cache_fmt == FB_BF16 || cache_fmt == FB_BFP8 || cache_fmt == FB_BFP4, "fb_prefill_attention: a bf16, bfp8 or bfp4 cache (dtype %d given)", cache_fmt);
+  FB_REQUIRE(q && cache && places && out && T >= 1 && T <= (1 << 20), "fb_prefill_attention: null pointer or no tokens");
+  FB_REQUIRE(hd == 64 || hd == 128, "fb_prefill_attention: heads of 64 or 128 columns (got %d)", hd);
+  FB_REQUIRE(KV >= 1 && H % KV == 0, "fb_prefill_attention: whole groups of query heads per key head (got %d / %d)", H, KV);
+  FB_REQUIRE(ld_q >= (int64_t)H * hd && ld_o >= (int64_t)H * hd && ld_q % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)cache % 16 == 0,
+             "fb_prefill_attention: rows of q 16-byte aligned");
+  FB_REQUIRE(first_row >= 0 && max_keys >= 1 && first_row + max_keys <= cache_rows && window >= 0, "fb_prefill_attention: the sequence's rows within the cache");
+  const bool packed = cache_fmt == FB_BFP8 || cache_fmt == FB_BFP4;
+  FB_REQUIRE(!packed || first_row % 64 == 0, "fb_prefill_attention: a sequence's rows start a packed unit (first_row a multiple of 64)");
+  FB_REQUIRE(packed || cache_head_stride >= cache_rows * hd, "fb_prefill_attention: heads at least cache_rows rows apart");
+  const int rep = H / KV;
+  fb::AttnArgs a{};
+  a.q = (const uint16_t*)q, a.q_s0 = (int64_t)rep * hd, a.q_s1 = hd, a.q_sr = ld_q;  // entry (key head, query head of its group): a row per token
+  if (packed) {
+    const int64_t head_bytes = fb::packed_bytes(cache_fmt, cache_rows, hd);
+    a.k = (const uint16_t*)cache, a.v = (const uint16_t*)((const uint8_t*)cache + KV * head_bytes), a.kv_s0 = head_bytes;
+  } else {
+    a.k = (const uint16_t*)cache, a.v = (const uint16_t*)cache + (int64_t)KV * cache_head_stride, a.kv_s0 = cache_head_stride;
+  }
+  a.kv_s1 = 0, a.base = nullptr, a.row0 = first_row, a.kv_rows = cache_rows;
+  a.place = places, a.p_s0 = 0, a.p_s1 = 0, a.p_sr = 1;
+  a.E1 = rep, a.rows = (int)T, a.window = window, a.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  a.out = (uint16_t*)out, a.o_s0 = (int64_t)rep * hd, a.o_s1 = hd, a.o_sr = ld_o;
+  return fb::launch_attention(a, H, hd, max_keys, workspace, workspace_bytes, (cudaStream_t)stream, packed ? cache_fmt : 0);
 }
 
 // ---- fb_decode_attention with its scratch built into the library -------------------------------------------------

@@ -27,7 +27,6 @@ namespace fb {
 namespace {
 
 constexpr int MW = 4, MTHREADS = 32 * MW, RED_LD = 132;  // warps per CTA; floats from one token's sums to the next's
-constexpr int WS_RSTD_BYTES = 1024;                      // workspace: 1/rms per token, then the normalised activations
 constexpr float UNDO_SCALE = 18446744073709551616.f;     // 2^64
 constexpr int STAGES = 6;                                // steps a warp keeps in flight (its ring in shared memory)
 constexpr int PREFETCH_UNITS = 16;                       // how far ahead of the loads the L2 prefetch runs (64-row units)
@@ -408,13 +407,13 @@ int linear_mma(const LinearArgs& args, cudaStream_t s) {
   MmaParams p{};
   p.a = args;
   if (args.norm_w) {
-    const size_t need = WS_RSTD_BYTES + (size_t)args.M * args.K * 2;
+    const size_t need = WS_BODY_AT + (size_t)args.M * args.K * 2;  // (linear.cuh: row scales at WS_RSTD_AT, the normalised activations after)
     if (!args.workspace || args.workspace_bytes < need) {
       set_error("fb_linear: workspace of %zu bytes needed, %zu given (fb_linear_workspace_bytes)", need, args.workspace_bytes);
       return FB_ERR_MEMORY;
     }
-    float* rstd = reinterpret_cast<float*>(args.workspace);
-    uint16_t* xn = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(args.workspace) + WS_RSTD_BYTES);
+    float* rstd = reinterpret_cast<float*>(static_cast<uint8_t*>(args.workspace) + WS_RSTD_AT);
+    uint16_t* xn = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(args.workspace) + WS_BODY_AT);
     mma_rms_prepare_kernel<<<(unsigned)args.M, 256, 0, s>>>(static_cast<const uint16_t*>(args.x), args.ldx,
                                                             static_cast<const uint16_t*>(args.norm_w), args.K, args.eps, xn, rstd);
     p.rstd = rstd, p.a.x = xn, p.a.ldx = args.K;

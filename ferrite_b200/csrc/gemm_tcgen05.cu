@@ -41,7 +41,8 @@ constexpr int TEAMS = 4;        // teams of worker warps, each unpacking every f
 constexpr int PREFETCH = 10;    // steps of K the L2 prefetch runs ahead
 constexpr int A_SLOT_BYTES = TILE_N * STEP_ROWS * 2;
 constexpr int MAX_STAGES = 8;
-constexpr int WS_RSTD = 1024;  // workspace: row scales, then the normalised activations
+// workspace (linear.cuh): arrival words of the persistent kernel's CTAs | row scales | partial tiles | normalised activations
+constexpr int MAX_GRID = (int)(WS_RSTD_AT - WS_ARRIVED_AT) / 4;
 
 struct GemmParams {
   LinearArgs a;
@@ -59,9 +60,15 @@ struct GemmParams {
   int n_experts, n_slots, steps_per_slot;
   int64_t expert_bytes, x_slot_rows, out_slot_stride;
   const uint16_t* row_scale;  // mode 1: bf16 [slot * M + t] multiplying the epilogue's result, or null
+  // the persistent kernel (a plain matmul): CTA c takes steps [c * work / grid, (c + 1) * work / grid) of the
+  // tiles x steps_total steps laid end to end; a tile shared by several CTAs meets in `partials` (fp32 [grid][nt][128],
+  // a CTA's own slot) with one arrival word per CTA in `arrived` (0 between launches)
+  int tiles, work;
+  float* partials;
+  uint32_t* arrived;
 };
 
-enum WaitCode { WAIT_X_EMPTY = 103, WAIT_X_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_ACC };
+enum WaitCode { WAIT_X_EMPTY = 103, WAIT_X_FULL, WAIT_A_EMPTY, WAIT_A_FULL, WAIT_ACC, WAIT_ACC_EMPTY, WAIT_SHARED_TILE };
 
 // a ring position: slot index and the parity of the phase its barriers are in (no division in the loops)
 struct Ring {
@@ -428,6 +435,349 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The plain matmul (no expert index) as a PERSISTENT kernel: one CTA per SM, and the tiles' steps of K laid end to end
+// (tile 0's steps, then tile 1's, ...) are cut into equal runs, one per CTA, so every SM streams the same number of
+// weight bytes whatever the tile count (224 tiles on 148 SMs would otherwise cost two rounds).  A CTA's run is a tail
+// of one tile, whole tiles, and a head of another: its SEGMENTS.  Weight loads, unpacking and MMAs run on across the
+// segment boundaries without a pause: the accumulators are double-buffered in tensor memory, and four warps of their
+// own (one per quarter of the TMEM lanes) empty a finished segment's while the next segment's MMAs fill the other pair:
+//   a whole tile:  epilogue straight from tensor memory;
+//   a tail (the run begins inside a tile):  the partial sums go to this CTA's slot of `partials` and its arrival word
+//                  is set - this is the FIRST segment of the CTA, so it is long done when it is needed;
+//   a head (the run ends inside a tile):  the LAST segment of the CTA; it owns the tile: waits (bounded) for the CTAs
+//                  after it that hold the rest of the tile, adds their partial sums to its own in CTA order - a fixed
+//                  order, so the result does not change from run to run - and runs the epilogue.
+// The wait is for CTAs with HIGHER numbers that did their part first, so it is short when the whole grid is resident
+// (grid <= SMs, one CTA each); were some CTA never to run, the wait gives up after its bound and reports.
+// Arrival words are cleared by the owner; the next launch touches them only after its griddep_wait(), i.e. after this
+// grid has finished.
+//
+// Warps: 0-15 unpack (4 teams), 16 and 17 issue MMAs, 18 feeds activations and the L2 prefetch, 19 idles, 20-23 run the
+// epilogues.  The unpacking warps need ~96 registers, the others few: the kernel is compiled for 768 threads (80 each)
+// and setmaxnreg moves registers from warps 16-19 to the unpacking warps.
+constexpr int P_THREADS = 24 * 32, WARP_EPI = 20;
+
+struct Segment {
+  int tile, k_first, k_steps;  // steps [k_first, k_first + k_steps) of the tile's p.steps_total
+  int i_first;                 // its first step, counted from the start of the CTA's run
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  constexpr int UNIT = unit_bytes(FMT), UNIT_MANT = unit_mant_bytes(FMT), RUN = run_bytes(FMT);
+  extern __shared__ uint8_t smem_unaligned[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int nt = p.nt, SX = p.x_slots, SA = p.a_slots;
+  const LinearArgs& a = p.a;
+  const bool swiglu = a.epilogue == FB_EPI_SWIGLU;
+  const int KS = (int)ksteps_of(a.K), G = (int)groups_of(a.N);
+  const int S = p.steps_total;
+
+  uint8_t* sA = smem;
+  const int x_slot_bytes = STEP_UNITS * nt * 128;
+  uint8_t* sX = sA + SA * A_SLOT_BYTES;
+  uint32_t* lut = reinterpret_cast<uint32_t*>(sX + SX * x_slot_bytes);
+  float* tok_rstd = reinterpret_cast<float*>(lut + 256);  // per token: the RMSNorm row scale (or 1), read by the epilogue warps only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tok_rstd + 128);
+  uint64_t* x_full = bars, *x_empty = bars + MAX_STAGES, *a_full = bars + 2 * MAX_STAGES, *a_empty = bars + 3 * MAX_STAGES;
+  uint64_t* acc_full = bars + 4 * MAX_STAGES, *acc_empty = acc_full + 2;  // one of each per accumulator pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  const uint32_t abort_flag = smem_u32(tmem_slot + 1);
+
+  griddep_launch_dependents();
+  if (tid == 0) {
+    for (int s = 0; s < SX; ++s) mbar_init(smem_u32(x_full + s), 1), mbar_init(smem_u32(x_empty + s), 1);
+    for (int s = 0; s < SA; ++s) mbar_init(smem_u32(a_full + s), WORKERS / 32 / TEAMS), mbar_init(smem_u32(a_empty + s), 1);
+    for (int b = 0; b < 2; ++b) mbar_init(smem_u32(acc_full + b), 2), mbar_init(smem_u32(acc_empty + b), 4);
+    tmem_slot[1] = 0;
+    fence_barrier_init();
+  }
+  if (tid < 256) lut[tid] = FMT == FB_BFP8 ? scale8(tid) : scale4(tid);
+  if (warp == WARP_MMA) tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  // this CTA's run of the work, and the work index -> (tile, step of K)
+  const int lo = (int)((int64_t)blockIdx.x * p.work / gridDim.x), hi = (int)((int64_t)(blockIdx.x + 1) * p.work / gridDim.x);
+  const int n_steps = hi - lo;
+  const int tile_lo = lo / S, k_lo = lo - tile_lo * S;
+  // (tile, step of K) of the run's step i, moved on by `by` steps at a time: no division in the loops
+  struct At {
+    int tile, ks;
+    __device__ __forceinline__ void advance(int by, int S) {
+      ks += by;
+      while (ks >= S) ks -= S, ++tile;
+    }
+  };
+  // segment number s of the run (0, 1, ...): the tile it lies in and its steps
+  auto segment = [&](int s) -> Segment {
+    Segment g;
+    g.tile = tile_lo + s;
+    g.k_first = s == 0 ? k_lo : 0;
+    g.i_first = s == 0 ? 0 : s * S - k_lo;
+    g.k_steps = min(S - g.k_first, n_steps - g.i_first);
+    return g;
+  };
+  const int n_segments = n_steps > 0 ? (k_lo + n_steps + S - 1) / S : 0;
+  // the two 64-column groups of a tile: neighbours, or a group of gate columns and the group of their up columns
+  auto groups = [&](int tile, int& g0, int& g1) { g0 = swiglu ? tile : 2 * tile, g1 = swiglu ? tile + G / 2 : 2 * tile + 1; };
+  const uint8_t* W = static_cast<const uint8_t*>(a.W);
+
+  if (warp < WORKERS / 32) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+    // ---- the unpacking warps: team t turns steps t, t + 4, ... of the run into bf16 A tiles, whatever tile they are of
+    constexpr int TEAM_THREADS = WORKERS / TEAMS;
+    const int team = tid / TEAM_THREADS, k = tid % TEAM_THREADS;
+    const int unit = k >> 6, ku = k & 63;
+    using RawT = typename std::conditional<FMT == FB_BFP8, uint4, uint2>::type;
+    const uint32_t sA32 = smem_u32(sA), lut32 = smem_u32(lut);
+    const uint32_t row_base = (uint32_t)((k >> 3) * 2 * 1024 + (k & 7) * 128);
+    Ring ra;
+    for (int t = 0; t < team; ++t) ra.next(SA);
+    RawT q[8];
+    uint32_t top[8];
+    // where step i's bytes lie for this thread's row of K: the number of its unit of each of the tile's two column
+    // groups, counted through the whole packed matrix (below 2^31: a matrix of under 4 TB); -1: zeros
+    auto locate = [&](int i, At at, int& u0, int& u1) {
+      u0 = u1 = -1;
+      if (i >= n_steps || at.ks * STEP_UNITS + unit >= KS) return;
+      int g0, g1;
+      groups(at.tile, g0, g1);
+      u0 = g0 * KS + at.ks * STEP_UNITS + unit;
+      if (g1 < G) u1 = g1 * KS + at.ks * STEP_UNITS + unit;
+    };
+    auto load = [&](int u0, int u1, int j) {  // run j of the tile: group j / 4, run j % 4 of it
+      const int u = (j >> 2) ? u1 : u0, run = j & 3;
+      if (u >= 0) {
+        const uint8_t* at = W + (int64_t)u * UNIT;
+        q[j] = __ldg(reinterpret_cast<const RawT*>(at + (run * KSTEP + ku) * RUN));
+        top[j] = __ldg(at + UNIT_MANT + run * KSTEP + ku);
+      } else {
+        q[j] = RawT{};
+        top[j] = 0;
+      }
+    };
+    At next{tile_lo, k_lo};  // where the step after this team's current one lies
+    next.advance(team, S);
+    {
+      int u0, u1;
+      locate(team, next, u0, u1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) load(u0, u1, j);
+    }
+    const uint32_t k7 = (uint32_t)(k & 7);
+    for (int i = team; i < n_steps; i += TEAMS) {
+      int n0, n1;
+      next.advance(TEAMS, S);
+      locate(i + TEAMS, next, n0, n1);
+      const int sa = ra.slot;
+      mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
+      const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t sc = ld_shared_u32(lut32 + top[j] * 4);
+        uint32_t v[8];
+        if constexpr (FMT == FB_BFP8) {
+          unpack8_word(q[j].x, sc, v[0], v[1]);
+          unpack8_word(q[j].y, sc, v[2], v[3]);
+          unpack8_word(q[j].z, sc, v[4], v[5]);
+          unpack8_word(q[j].w, sc, v[6], v[7]);
+        } else {
+          unpack4_word(q[j].x, sc, v);
+          unpack4_word(q[j].y, sc, v + 4);
+        }
+        load(n0, n1, j);  // this register's next bytes are on their way while the rest of the step is unpacked
+        const int sl = swiglu ? ((j & 3) << 1 | j >> 2) : j;  // gate and up runs alternate: rows r and r + 16 pair up
+        const uint32_t at = slot + (sl >> 2) * 1024;
+        const uint32_t c0 = (uint32_t)(sl & 3) * 2;
+        st_shared_v4(at + ((c0 ^ k7) << 4), v[0], v[1], v[2], v[3]);
+        st_shared_v4(at + (((c0 + 1) ^ k7) << 4), v[4], v[5], v[6], v[7]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+      for (int t = 0; t < TEAMS; ++t) ra.next(SA);
+    }
+  } else if (warp < WARP_EPI) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+    if (warp == WARP_X && lane <= PREFETCH) {
+      Ring rx;
+      // packed weights PREFETCH steps ahead into L2 (see the kernel above)
+      auto prefetch = [&](int step, At at) {
+        if (step >= n_steps) return;
+        const int first = at.ks * STEP_UNITS, units = min(STEP_UNITS, KS - first);
+        if (units <= 0) return;
+        int g0, g1;
+        groups(at.tile, g0, g1);
+        bulk_prefetch_l2(W + (int64_t)(g0 * KS + first) * UNIT, units * UNIT);
+        if (g1 < G) bulk_prefetch_l2(W + (int64_t)(g1 * KS + first) * UNIT, units * UNIT);
+      };
+      At ahead{tile_lo, k_lo};  // the step the prefetch has reached
+      if (lane == 0) {
+        prefetch_tensormap(&tmap_x);
+        ahead.advance(PREFETCH, S);
+      } else {
+        ahead.advance(lane - 1, S);
+        prefetch(lane - 1, ahead);  // the first steps' bytes, asked for by a lane each
+      }
+      if (lane == 0) griddep_wait();  // the activations come from the kernel before
+      int ks = k_lo;
+      for (int i = 0; lane == 0 && i < n_steps; ++i, rx.next(SX)) {
+        const int s = rx.slot;
+        mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
+        mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
+#pragma unroll
+        for (int u = 0; u < STEP_UNITS; ++u)
+          tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, ks * STEP_ROWS + u * KSTEP, 0, smem_u32(x_full + s));
+        if (++ks == S) ks = 0;
+        prefetch(i + PREFETCH, ahead);
+        ahead.advance(1, S);
+      }
+    } else if ((warp == WARP_MMA || warp == WARP_MMA + 1) && lane == 0) {
+      const int me = warp - WARP_MMA;  // steps me, me + 2, ... of the run; segment s into accumulator me of pair s % 2
+      const uint32_t idesc = umma_idesc_bf16(nt, true, false);
+      const uint64_t da0 = umma_smem_desc(smem_u32(sA), 1024, 2048), dx0 = umma_smem_desc(smem_u32(sX), 16, 1024);
+      const uint32_t x_slot16 = (uint32_t)x_slot_bytes >> 4, x_unit16 = (uint32_t)(nt * 128) >> 4;
+      Ring ra, rx;
+      if (me) ra.next(SA), rx.next(SX);
+      int i = me;
+      for (int s = 0; s < n_segments; ++s) {
+        const Segment g = segment(s);
+        const int i_end = g.i_first + g.k_steps, pair = s & 1;
+        const uint32_t acc = tmem + (2 * pair + me) * nt;
+        if (s >= 2) {  // the pair is free once the epilogue of the segment before last has read it
+          mbar_wait(smem_u32(acc_empty + pair), (uint32_t)((s >> 1) - 1) & 1, abort_flag, WAIT_ACC_EMPTY);
+          tc_fence_after();
+        }
+        uint32_t started = 0;
+        for (; i < i_end; i += 2, ra.next(SA), ra.next(SA), rx.next(SX), rx.next(SX)) {
+          mbar_wait(smem_u32(a_full + ra.slot), ra.phase, abort_flag, WAIT_A_FULL);
+          mbar_wait(smem_u32(x_full + rx.slot), rx.phase, abort_flag, WAIT_X_FULL);
+          tc_fence_after();
+          const uint64_t da = da0 + (uint32_t)ra.slot * (A_SLOT_BYTES >> 4), dx = dx0 + (uint32_t)rx.slot * x_slot16;
+#pragma unroll
+          for (int kk = 0; kk < STEP_ROWS / 16; ++kk)
+            umma_bf16(acc, da + kk * (4096 >> 4), dx + (kk >> 2) * x_unit16 + (kk & 3) * (32 >> 4), idesc, started | kk);
+          started = 1;
+          umma_commit(smem_u32(a_empty + ra.slot));
+          umma_commit(smem_u32(x_empty + rx.slot));
+        }
+        umma_commit(smem_u32(acc_full + pair));  // (one arrival per issuer and segment, whether or not it had a step in it)
+      }
+    }
+  } else {
+    // ---- the epilogue warps: warp 20 + q reads quarter q of the TMEM lanes (tile rows 32q .. 32q + 31), all tokens
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
+    const int qd = warp - WARP_EPI, row = 32 * qd + lane, etid = tid - WARP_EPI * 32;
+    griddep_wait();  // the row scales, the residual and the arrival words are the work of kernels before this one
+    for (int t = etid; t < 128; t += 128) tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    for (int s = 0; s < n_segments; ++s) {
+      const Segment g = segment(s);
+      const int pair = s & 1;
+      const bool whole_end = g.k_first + g.k_steps == S;  // the segment reaches the tile's last step
+      const bool tail = g.k_first > 0;                    // it does not start the tile: its sums go to the tile's owner
+      const int64_t n = swiglu ? 64 * (int64_t)g.tile + 16 * qd + (lane & 15) : TILE_N * (int64_t)g.tile + row;
+      const bool live = swiglu ? lane < 16 && n < a.N / 2 : n < a.N;
+      // the CTAs after this one that hold the rest of an owned tile: c + 1 .. while their runs begin inside the tile
+      int others = 0;
+      if (!tail && !whole_end) {
+        const int64_t tile_end = (int64_t)(g.tile + 1) * S;
+        while ((int)blockIdx.x + others + 1 < (int)gridDim.x && (int64_t)(blockIdx.x + others + 1) * p.work / gridDim.x < tile_end) ++others;
+      }
+      mbar_wait(smem_u32(acc_full + pair), (uint32_t)(s >> 1) & 1, abort_flag, WAIT_ACC);
+      tc_fence_after();
+      for (int o = lane; o < others; o += 32) {  // a lane per CTA waited for (every epilogue warp waits for itself)
+        const uint32_t* flag = p.arrived + blockIdx.x + 1 + o;
+        const long long start = clock64();
+        for (;;) {
+          uint32_t v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (v || ld_shared_volatile(abort_flag)) break;
+          if (clock64() - start > WAIT_CLOCKS) {
+            asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
+            atomicCAS(&g_status_word, 0, (int)WAIT_SHARED_TILE);
+            break;
+          }
+          __nanosleep(32);
+        }
+      }
+      __syncwarp();
+      const bool even = g.k_steps > 1 || !(g.i_first & 1), odd = g.k_steps > 1 || (g.i_first & 1);  // which accumulators hold steps
+      const uint32_t acc = tmem + ((uint32_t)(32 * qd) << 16) + 2 * pair * nt;
+      float* mine = p.partials + (size_t)blockIdx.x * nt * TILE_N;
+      // 16 tokens at a time, and within them every load of a kind issued before the first is used: an epilogue is a
+      // few trips to memory (residual, the other CTAs' partial sums), not one per eight tokens
+      for (int c0 = 0; c0 < nt && c0 < a.M; c0 += 16) {
+        float v[16], res[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int t = c0 + e;
+          res[e] = !tail && live && t < a.M && a.epilogue == FB_EPI_RESIDUAL
+                       ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[t * a.ldr + n]) : 0.f;
+        }
+#pragma unroll
+        for (int cb = 0; cb < 16; cb += 8) {  // (nt is a multiple of 16)
+          if (even) tmem_ld8(acc + c0 + cb, v + cb);
+          if (odd) {
+            float w[8];
+            tmem_ld8(acc + nt + c0 + cb, w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[cb + e] = even ? v[cb + e] + w[e] : w[e];
+          }
+        }
+        if (tail) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
+          continue;
+        }
+        for (int o = 0; o < others; ++o) {  // the rest of the tile, in CTA order
+          const float* theirs = p.partials + (size_t)(blockIdx.x + 1 + o) * nt * TILE_N + (size_t)c0 * TILE_N + row;
+          float w[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) w[e] = c0 + e < a.M ? __ldcg(theirs + e * TILE_N) : 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] += w[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int t = c0 + e;  // (the same for the whole warp)
+          if (t >= a.M) break;
+          float val = v[e] * tok_rstd[t];
+          if (swiglu) {
+            const float up = __shfl_down_sync(0xffffffffu, val, 16);
+            val = val / (1.f + __expf(-val)) * up;
+          } else {
+            val += res[e];
+          }
+          if (!live) continue;
+          const int64_t at = t * a.ldo + n;
+          if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = val;
+          else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(val);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(acc_empty + pair));  // this warp's quarter of the pair has been read
+      if (tail || others) {  // the four warps' partial sums are out / have been read: say so, once
+        if (tail) __threadfence();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (etid == 0 && tail) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.arrived + blockIdx.x), "r"(1u) : "memory");
+        if (etid < others) p.arrived[blockIdx.x + 1 + etid] = 0;  // read: ready for the next launch
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem, p.tmem_cols);
+  }
+}
+
 // x' = bf16(x * g) and rstd[t] = rsqrt(mean(x^2) + eps): the RMSNorm prologue's two factors, once per call.
 // The row scale commutes with the matmul, so the GEMM applies it to the accumulators.
 __global__ void __launch_bounds__(256) rms_prepare_kernel(const uint16_t* __restrict__ x, int64_t ldx, const uint16_t* __restrict__ g,
@@ -535,10 +885,49 @@ bool linear_tcgen05_supports(const LinearArgs& a) {
          (a.epilogue != FB_EPI_SWIGLU || a.N % 128 == 0);
 }
 
+// SMs of the current device (the persistent kernel's grid never exceeds it: every CTA must be resident)
+static int sm_count() {
+  static int known[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!known[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 1, cudaGetLastError();
+    known[dev] = n < MAX_GRID ? n : MAX_GRID;
+  }
+  return known[dev];
+}
+
+static size_t partials_bytes(int64_t M) {
+  const int64_t rows = M < 128 ? M : 128, nt = (rows + 15) / 16 * 16;
+  return (size_t)MAX_GRID * nt * TILE_N * sizeof(float);
+}
+
+bool linear_persistent_wins(const LinearArgs& a) {
+  (void)a;
+  return false;  // (measured: not yet - the per-tile kernel is ahead on every shape of the benchmark)
+}
+
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N) {
   (void)N;
   if (M < 1) return 0;
-  return WS_RSTD + (size_t)(M < 128 ? M : 128) * K * 2;
+  return WS_BODY_AT + partials_bytes(M) + (size_t)(M < 128 ? M : 128) * K * 2;
+}
+
+// The persistent kernel's grid: the CTA count with the least modelled time - a CTA's fixed cost, its steps, and, where
+// tiles are shared between CTAs, the owner's wait and its reads of the other CTAs' partial sums.
+static int persistent_grid(int tiles, int steps) {
+  const int64_t work = (int64_t)tiles * steps;
+  const int most = (int)(work < sm_count() ? work : sm_count());
+  int best = 1;
+  double best_cost = 1e30;
+  for (int g = 1; g <= most; ++g) {
+    const int per = (int)ceil_div(work, g);
+    const bool shared = work % g != 0 || per % steps != 0;  // some run begins or ends inside a tile
+    const double cost = 0.5 * per + (shared ? 1.0 + 0.25 * (double)(ceil_div(steps, per) < g ? ceil_div(steps, per) : g) : 0.0);
+    if (cost < best_cost - 1e-9) best_cost = cost, best = g;
+  }
+  return best;
 }
 
 static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) {
@@ -555,14 +944,17 @@ static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) 
   p.x_slots = pl.x_slots, p.a_slots = pl.a_slots;
   const void* x = a.x;
   int64_t ldx = a.ldx;
-  if (a.norm_w) {
-    const size_t need = WS_RSTD + (size_t)a.M * a.K * 2;
+  const size_t shared_tiles = mode == 0 && a.persistent ? partials_bytes(a.M) : 0;
+  if (a.norm_w || shared_tiles) {
+    const size_t need = WS_BODY_AT + shared_tiles + (a.norm_w ? (size_t)a.M * a.K * 2 : 0);
     if (!a.workspace || a.workspace_bytes < need) {
       set_error("fb_linear: workspace of %zu bytes needed, %zu given (fb_linear_workspace_bytes)", need, a.workspace_bytes);
       return FB_ERR_MEMORY;
     }
-    float* rstd = reinterpret_cast<float*>(a.workspace);
-    uint16_t* xn = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(a.workspace) + WS_RSTD);
+  }
+  if (a.norm_w) {
+    float* rstd = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + WS_RSTD_AT);
+    uint16_t* xn = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(a.workspace) + WS_BODY_AT + shared_tiles);
     rms_prepare_kernel<<<(unsigned)a.M, 256, 0, s>>>(static_cast<const uint16_t*>(a.x), a.ldx, static_cast<const uint16_t*>(a.norm_w), a.K,
                                                      a.eps, xn, rstd);
     p.rstd = rstd, x = xn, ldx = a.K;
@@ -579,12 +971,26 @@ static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) 
     set_error("fb_linear: cuTensorMapEncodeTiled failed (%d) for x [%lld, %lld] stride %lld", (int)rc, (long long)a.M, (long long)a.K, (long long)ldx);
     return FB_ERR_LAUNCH;
   }
-  auto kernel = a.fmt == FB_BFP8 ? linear_tcgen05_kernel<FB_BFP8> : linear_tcgen05_kernel<FB_BFP4>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[a.fmt == FB_BFP8]) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    attr_set[a.fmt == FB_BFP8] = true;
+  if (mode == 0 && a.persistent) {  // a plain matmul by the persistent kernel: the tiles' steps shared out evenly over the SMs
+    auto persistent = a.fmt == FB_BFP8 ? linear_persistent_kernel<FB_BFP8> : linear_persistent_kernel<FB_BFP4>;
+    static std::atomic<uint64_t> opted[2];
+    if (first_on_device(opted[a.fmt == FB_BFP8])) cudaFuncSetAttribute(persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    p.splits = 1, p.tiles = pl.tiles, p.work = pl.tiles * pl.steps;
+    p.tmem_cols = 4 * pl.nt <= 64 ? 64 : 4 * pl.nt <= 128 ? 128 : 4 * pl.nt <= 256 ? 256 : 512;  // two pairs of accumulators
+    p.arrived = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a.workspace) + WS_ARRIVED_AT);
+    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + WS_BODY_AT);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(persistent_grid(pl.tiles, pl.steps)), cfg.blockDim = dim3(P_THREADS), cfg.dynamicSmemBytes = pl.smem, cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the kernel before it drains
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, persistent, tmap, p) != cudaSuccess) return launch_status("fb_linear (tcgen05 launch)");
+    return launch_status("fb_linear (tcgen05)");
   }
+  auto kernel = a.fmt == FB_BFP8 ? linear_tcgen05_kernel<FB_BFP8> : linear_tcgen05_kernel<FB_BFP4>;
+  static std::atomic<uint64_t> opted_indexed[2];
+  if (first_on_device(opted_indexed[a.fmt == FB_BFP8])) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.tiles, pl.splits, mode == 1 ? slots : 1), cfg.blockDim = dim3(THREADS), cfg.dynamicSmemBytes = pl.smem, cfg.stream = s;
   cudaLaunchAttribute attr[2];

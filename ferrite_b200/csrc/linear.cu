@@ -5,7 +5,7 @@
 static int g_linear_kernel = FB_LINEAR_AUTO;
 
 extern "C" int fb_linear_prefer(int kernel) {
-  FB_REQUIRE(kernel >= FB_LINEAR_AUTO && kernel <= FB_LINEAR_MMA, "fb_linear_prefer: unknown kernel %d", kernel);
+  FB_REQUIRE(kernel >= FB_LINEAR_AUTO && kernel <= FB_LINEAR_PERSISTENT, "fb_linear_prefer: unknown kernel %d", kernel);
   g_linear_kernel = kernel;
   return FB_OK;
 }
@@ -38,7 +38,8 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
   // its legacy MMAs cost about 27 cycles each per SM quarter, so beyond 8 rows the tcgen05 kernel is faster)
   const bool few_rows_win = M > 1 && M <= 8 && K <= 8192 && (fmt == FB_BFP4 || K * N <= (int64_t)32 << 20);
   if (prefer == FB_LINEAR_AUTO && few_rows_win && fb::linear_mma_supports(a)) return fb::linear_mma(a, s);
-  if (M > 1 && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);
+  a.persistent = prefer == FB_LINEAR_PERSISTENT || (prefer == FB_LINEAR_AUTO && fb::linear_persistent_wins(a));
+  if ((M > 1 || prefer == FB_LINEAR_PERSISTENT) && fb::linear_tcgen05_supports(a)) return fb::linear_tcgen05(a, s);
   return fb::linear_gemv(a, s);
 }
 

@@ -20,6 +20,7 @@ struct LinearArgs {
   int64_t ldr;
   void* workspace;
   size_t workspace_bytes;
+  bool persistent = false;  // the tcgen05 path's persistent kernel (tiles' steps shared out over the SMs) instead of a CTA per tile
 };
 
 // Tensor.matmul(index=) (ferrite/tensor.py:450-460): W a batch of packed matrices, index[slot] picks one per slot
@@ -32,12 +33,20 @@ struct IndexedArgs {
   const void* row_scale;    // mode 1: bf16 [slot * M + t] multiplying the epilogue's result, or null
 };
 
+// fb_linear's workspace, shared by its kernels (calls on one stream run in order):
+//   [0, 1024)     arrival words of the persistent tcgen05 kernel's CTAs: zero before the first call, and every call
+//                 leaves them zero - nothing else may ever be written here;
+//   [1024, 2048)  the row scales of an RMSNorm prologue;
+//   [2048, ...)   each kernel's own: partial tiles, the normalised activations.
+constexpr size_t WS_ARRIVED_AT = 0, WS_RSTD_AT = 1024, WS_BODY_AT = 2048;
+
 int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: one token (up to 4 a pass), CUDA cores
 int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores (tcgen05, tiles through shared memory)
 int linear_mma(const LinearArgs& a, cudaStream_t s);      // gemm_mma.cu: up to 32 tokens, tensor cores fed from registers
 bool linear_mma_supports(const LinearArgs& a);
 int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStream_t s);
 bool linear_tcgen05_supports(const LinearArgs& a);
+bool linear_persistent_wins(const LinearArgs& a);  // whether fb_linear, left to choose, runs the persistent kernel for this shape
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N);
 
 }  // namespace fb

@@ -96,7 +96,54 @@ __global__ void __launch_bounds__(256) touched_kernel(const int32_t* __restrict_
   }
 }
 
+// One block of n threads (rounded up to whole warps), a thread per value (expert): Tensor.group's counting sort.  Thread
+// e counts its choices, the runs' first slots are a scan over the counts rounded up to whole tiles of 32, and thread e
+// hands its choices their slots in the choices' own order (row by row, choice by choice), as the reference's one-worker
+// kernel does (ferrite/compiler.py:1844-1896) - so the result is that kernel's, slot for slot.
+__global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__ ids, int rows, int k, int n, int t, int rp,
+                                                     int32_t* __restrict__ order, int32_t* __restrict__ tiles, int32_t* __restrict__ places) {
+  griddep_launch_dependents();
+  extern __shared__ int32_t first_slot[];  // [n + 1]
+  const int e = threadIdx.x, total = rows * k;
+  for (int s = threadIdx.x; s < 32 * t; s += blockDim.x) order[s] = 0;
+  for (int i = threadIdx.x; i < t; i += blockDim.x) tiles[i] = n;  // none: a matmul picking by them skips the tiles past those used
+  for (int s = threadIdx.x; s < k * rp; s += blockDim.x) places[s] = 0;
+  int count = 0;
+  if (e < n)
+    for (int i = 0; i < total; ++i) count += ids[i] == e;  // (every thread reads the same word: a broadcast)
+  if (e <= n) first_slot[e] = e < n ? (count + 31) / 32 * 32 : 0;
+  __syncthreads();  // (also: the fills above are done before any slot is written)
+  if (threadIdx.x == 0) {  // the runs one after another, each a whole number of tiles
+    int s = 0;
+    for (int v = 0; v <= n; ++v) {
+      const int room = first_slot[v];
+      first_slot[v] = s;
+      s += room;
+    }
+  }
+  __syncthreads();
+  if (e >= n) return;
+  int s = first_slot[e];
+  for (int tile = s / 32; tile < first_slot[e + 1] / 32; ++tile) tiles[tile] = e;
+  for (int i = 0; i < total && count; ++i)
+    if (ids[i] == e) {
+      const int r = i / k, j = i - r * k;
+      order[s] = r;
+      places[j * rp + r] = s;
+      ++s, --count;
+    }
+}
+
 }  // namespace fb
+
+extern "C" int fb_group(const int32_t* ids, int64_t rows, int k, int n, int32_t* order, int32_t* tiles, int32_t* places, void* stream) {
+  FB_REQUIRE(ids && order && tiles && places && rows >= 1 && k >= 1 && k <= 32 && n >= 1 && n <= 1023, "fb_group: up to 32 choices a row of up to 1023 values");
+  FB_REQUIRE(rows * k <= (1 << 22), "fb_group: up to 4 M choices");
+  const int64_t t = (rows * k + 31) / 32 + (n < rows * k ? n : rows * k), rp = (rows + 31) / 32 * 32;
+  const int threads = (n + 1 + 31) / 32 * 32;
+  fb::group_kernel<<<1, threads, (size_t)(n + 1) * sizeof(int32_t), (cudaStream_t)stream>>>(ids, (int)rows, k, n, (int)t, (int)rp, order, tiles, places);
+  return fb::launch_status("fb_group");
+}
 
 extern "C" int fb_topk(int dtype, const void* x, int64_t rows, int64_t cols, int64_t ldx, int k, const int32_t* labels, void* values,
                        int32_t* ids, void* softmax_weights_bf16, int64_t ldo, void* stream) {

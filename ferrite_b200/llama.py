@@ -29,13 +29,26 @@ def head(c):
     return c.head_dim or c.dim // c.heads
 
 
-def precision(c, mode="bf16"):
-    """{(op, block): (format, phases)} (models/llama.py:54-76); the phases are kept for the signature and ignored."""
-    four = {"bfp4": ("gate_up",), "experts": ("gate_up", "down")}.get(mode, ())
+def precision(c, mode="bf16", kv=None):
+    """{(op, block): (format, phases)} (models/llama.py:54-76); the phases are kept for the signature and ignored (the
+    products are exact here).  kv: the KV cache's format, under ("kv", None): bf16 unless said, bfp8 for the reference's
+    fast modes ("tt", "experts")."""
+    four = {"bfp4": ("gate_up",), "tt": ("gate_up",), "experts": ("gate_up", "down")}.get(mode, ())
     fmt = lambda op: mode if mode in ("bf16", "bfp8") else ("bfp4" if op in four else "bfp8")
     p = {(op, l): (fmt(op), 4) for l in range(c.layers) for op in ("qkv", "o", "gate_up", "down")}
     p["head", None] = (fmt("head"), 4)
+    p["kv", None] = (kv or ("bfp8" if mode in ("tt", "experts") else "bf16"), None)
     return p
+
+
+def precision_of(c, op, block=None):
+    """(format, phases) of op in block under c.precision, None for either unless said (models/llama.py:78)."""
+    return (getattr(c, "precision", None) or {}).get((op, block), (None, None))
+
+
+def cache_format(c):
+    """The KV cache's format under c.precision (models/llama.py:80)."""
+    return precision_of(c, "kv")[0] or "bf16"
 
 
 def weight_format(name, prec):
@@ -88,7 +101,8 @@ def attention(h, p, c, rotary, seen, cache, rows, slots=None):
     base, last, length, window = seen
     qkv = h.matmul(p["qkv_proj"])
     q = qkv.rope_put(cos, sin, places, rows, cache, c.heads, c.kv, p.get("qk_norm"), c.eps)
-    o = q.attend_cache(cache, base, last, c.kv, length, window)
+    # (a prompt's chunk - several tokens of one sequence - shares its key rows between the tokens of a query head)
+    o = q.attend_cache(cache, base, last, c.kv, length, window, chunk=slots is None and q.rows > 1)
     return o.matmul(p["o_proj"])
 
 
@@ -112,10 +126,29 @@ def experts(h, p, ids, w, c=None):
     gate_up, down = p["experts.gate_up"], p["experts.down"]
     m, e = down.rows, gate_up.batch
     tp = getattr(c, "tp", None)
-    picks, weights = ids.touched(e, w.bfloat16().realize(), first=tp.rank * e if tp else 0)
-    x = h.matmul(gate_up, index=picks)
-    g = glu(x[:, :, :m], x[:, :, m:])
-    return (g * weights).matmul(down, index=picks).sum(0)
+    first, n, k = tp.rank * e if tp else 0, ids.rows, ids.cols
+    if n <= 128:  # a decode step: every touched expert an entry, all the tokens its rows (models/llama.py:317-324)
+        picks, weights = ids.touched(e, w.bfloat16().realize(), first=first)
+        x = h.matmul(gate_up, index=picks)
+        g = glu(x[:, :, :m], x[:, :, m:])
+        return (g * weights).matmul(down, index=picks).sum(0)
+    # a prompt: each expert's tokens grouped into whole tiles of 32, a batch entry a tile, each token's k outputs gathered
+    # back, weighted and summed (models/llama.py:318-320, 325-329).  A rank that holds some of the experts groups only the
+    # choices among its own; the others' weigh 0 here and are added by the ranks that hold them.
+    w = w.bfloat16().realize()
+    if tp:
+        mine = ((ids >= first) * (ids < first + e)).realize()
+        ids, w = ((ids - first) * mine + (1 - mine) * e).realize(), (w * mine.bfloat16()).realize()
+    order, picks, places = ids.group(e)
+    x = h.realize().gather(order).split(picks.rows, 1)
+    x = x.matmul(gate_up, index=picks).realize()
+    y = glu(x[:, :, :m], x[:, :, m:]).matmul(down, index=picks).realize().reshape(order.cols, down.cols)
+    run = places.cols // k
+    terms = [y.gather(places[:, :, j * run:j * run + n]) * w[:, :, j:j + 1] for j in range(k)]
+    out = terms[0]
+    for term in terms[1:]:
+        out = out + term
+    return out
 
 
 def layer(x, p, c, rotary, seen, cache, rows, live=None, slots=None):
@@ -281,6 +314,14 @@ def prefill(ids, w, c, caches, tokens, on):
 def kv_cache(c, size, zeros, slots=1):
     """Each block's keys' heads then its values', a row for each of size places (models/llama.py:506-514)."""
     return [zeros((2 * c.kv, size, head(c))) for _ in range(c.layers)]
+
+
+def slot(c, caches, u, slots):
+    """Caches made for several sequences (slots) as sequence u's alone, in place: its part of each block's cache
+    (models/llama.py:520-526).  bf16 caches (a view); a block-float cache's sequences are addressed by their first rows
+    (forward's slots) instead."""
+    assert all(kv.dtype not in BFP for kv in caches), "a view of a block-float cache's rows: run the sequences together (slots) instead"
+    return [kv[:, u * kv.rows // slots:(u + 1) * kv.rows // slots, :] for kv in caches]
 
 
 def zeros(rt, dtype="bf16"):

@@ -174,6 +174,24 @@ def decode_attention(q, cache, base, place, H, KV, hd, max_keys, window=0, out=N
     return out
 
 
+def prefill_attention(q, cache, first_row, places, H, KV, hd, max_keys, window=0, out=None):
+    """A chunk of one sequence's prompt: token t (at places[t]) attends the cache rows first_row .. first_row + places[t]
+    of its kv head; 16 tokens of a query head share every key row read."""
+    T = q.shape[0]
+    packed = isinstance(cache, Packed)
+    assert q.dtype == torch.bfloat16 and q.shape[1] == H * hd and q.stride(1) == 1 and places.dtype == torch.int32 and places.numel() == T
+    assert (cache.batch == 2 * KV and cache.N == hd) if packed else (cache.stride(2) == 1 and cache.stride(1) == hd)
+    if out is None:
+        out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=q.device)
+    need = lib().fb_prefill_attention_workspace_bytes(T, H, hd, max_keys)
+    ws = attention_workspace(q.device, need)
+    check(lib().fb_prefill_attention(cache.code if packed else BF16, q.data_ptr(), T, q.stride(0), H, KV, hd, cache.data.data_ptr() if packed else cache.data_ptr(),
+                                     cache.K if packed else cache.shape[1], 0 if packed else cache.stride(0), first_row, places.data_ptr(), max_keys, window,
+                                     out.data_ptr(), out.stride(0), _ptr(ws) if need else None, ws.numel() if need else 0, _stream()))
+    count(2 if need else 1)
+    return out
+
+
 def rmsnorm(x, w, eps=1e-5, out=None):
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and w.numel() == x.shape[1]
     if out is None:

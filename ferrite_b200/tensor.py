@@ -224,6 +224,10 @@ class Tensor:
         k = 2 * math.sqrt(2 / math.pi)
         return self * (1 + (self * (self * self * (-0.044715 * k) - k)).exp()).reciprocal()
 
+    def delta(self, *args, **kwargs):
+        """Gated DeltaNet's recurrence (ferrite/tensor.py): on the reference's surface, not on the decode path built here."""
+        raise NotImplementedError("Tensor.delta (Gated DeltaNet) is outside the decode path this library covers")
+
     def sum(self, axis=None): return self._reduce("sum", axis)
     def max(self, axis=None): return self._reduce("max", axis)
 
@@ -359,9 +363,12 @@ class Tensor:
 
     def gather(self, ids):
         """Rows ids of this matrix: an embedding lookup (ferrite/tensor.py:116-126)."""
-        if not isinstance(ids, Tensor):
-            assert all(0 <= i < self.rows for i in ids)
-            ids = Tensor.of(self.rt, [list(ids)], "int32")
+        if not isinstance(ids, Tensor):  # a list of rows: a constant of the program, uploaded once (a recorded step meets it again)
+            key = ("rows", tuple(int(i) for i in ids))
+            assert all(0 <= i < self.rows for i in key[1])
+            if key not in self.rt.numbers:
+                self.rt.numbers[key] = Tensor.of(self.rt, [list(key[1])], "int32")
+            ids = self.rt.numbers[key]
         assert self.batch == 1 and ids.dtype == "int32" and ids.shape[:2] == (1, 1), "rows of a matrix, by a row of int32"
         t, ids = self.realize(), ids.realize()
         table = t.buf[0] if t.buf[0].is_contiguous() else t.buf[0].contiguous()
@@ -451,6 +458,21 @@ class Tensor:
         self.rt.launched("topk", 1)
         return values, ids
 
+    def group(self, n):
+        """A mixture of experts' tokens grouped by expert, from int32 choices (rows x k, values below n), as three int32
+        tensors (ferrite/tensor.py:389-402): order, a row of 32 t slots in which each value's choices have a run of whole
+        tiles of 32, each slot the row it holds (0 for none); tiles, a column of t, each tile's value (n past those
+        used); places, a row of k runs of the rows rounded up to 32, run j holding the slot of each row's choice j."""
+        assert self.dtype == "int32" and self.batch == 1 and self.cols <= 32, "a matrix of int32 choices, at most 32 a row"
+        x = self.realize()
+        x = x if x.buf.is_contiguous() else (x + 0).realize()
+        rows, k = self.rows, self.cols
+        t, rp = -(-rows * k // 32) + min(n, rows * k), -(-rows // 32) * 32
+        order, tiles, places = Tensor(self.rt, 1, 32 * t, dtype="int32"), Tensor(self.rt, t, 1, dtype="int32"), Tensor(self.rt, 1, k * rp, dtype="int32")
+        check(lib().fb_group(x.buf.data_ptr(), rows, k, n, order.buf.data_ptr(), tiles.buf.data_ptr(), places.buf.data_ptr(), ops._stream()))
+        self.rt.launched("group", 1)
+        return order, tiles, places
+
     def touched(self, n, weights, first=0):
         """The experts some row picks by a weight that is not 0, each once, ascending, then n (none); and each entry's
         weight from each row (ferrite/tensor.py:403-416).  first: count the experts from it (a rank's run of a mixture's
@@ -486,18 +508,24 @@ class Tensor:
         self.rt.launched("rope put")
         return out
 
-    def attend_cache(self, cache, base, last, kv, length=None, window=0):
+    def attend_cache(self, cache, base, last, kv, length=None, window=0, chunk=False):
         """self: [1, tokens, heads hd], each token's query heads.  Token t attends the cache rows base[t] .. base[t] +
         last[t] of every kv head (the last `window` of them, if any), its heads / kv query heads sharing each key row
         read: attention as models/llama.py:129-146 runs it on the chip (Tensor.attend with places), without the views,
         the repeat and the regrouping moves in between.  length: the most keys a token can see (it sizes the split of
-        the keys over the GPU)."""
+        the keys over the GPU).  chunk: the tokens are one sequence's (a prompt's chunk, its first cache row 0): a query
+        head's tokens then share each key row read, 16 at a time, instead of every token reading the keys anew."""
         hd = cache.cols
         q = self.realize()
         heads = q.cols // hd
         assert q.batch == 1 and q.cols % hd == 0 and heads % kv == 0 and cache.batch == 2 * kv, f"{q.shape} over a cache {cache.shape}"
         base, last = base.realize(), last.realize()
         out = Tensor(self.rt, q.rows, q.cols)
+        if chunk:
+            ops.prefill_attention(q.buf[0], cache.packed if cache.dtype in BFP else cache.buf, 0, last.buf.reshape(-1), heads, kv, hd,
+                                  max_keys=min(length or cache.rows, cache.rows), window=window or 0, out=out.buf[0])
+            self.rt.launched("attention")
+            return out
         ops.decode_attention(q.buf[0], cache.packed if cache.dtype in BFP else cache.buf, base.buf.reshape(-1), last.buf.reshape(-1), heads, kv, hd,
                              max_keys=min(length or cache.rows, cache.rows),
                              window=window or 0, out=out.buf[0])

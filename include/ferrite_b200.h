@@ -111,8 +111,10 @@ int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const v
  * stated for each).  FB_LINEAR_AUTO (the default) chooses by M as described above; FB_LINEAR_TCGEN05 and
  * FB_LINEAR_GEMV restore the choice without the register-fed kernel (GEMV up to 4 rows when asked for, else one row);
  * FB_LINEAR_MMA sends every shape the register-fed kernel supports (M <= 32, K a multiple of 16) to it, one row too.
+ * FB_LINEAR_PERSISTENT runs the tcgen05 path as one persistent CTA per SM, the tiles' steps of K shared out evenly and
+ * tiles that several CTAs share summed through the workspace in a fixed order (one row too).
  * The reference has one matmul kernel and no such switch (ferrite/compiler.py:699-738). */
-enum fb_linear_kernel { FB_LINEAR_AUTO = 0, FB_LINEAR_TCGEN05 = 1, FB_LINEAR_GEMV = 2, FB_LINEAR_MMA = 3 };
+enum fb_linear_kernel { FB_LINEAR_AUTO = 0, FB_LINEAR_TCGEN05 = 1, FB_LINEAR_GEMV = 2, FB_LINEAR_MMA = 3, FB_LINEAR_PERSISTENT = 4 };
 int fb_linear_prefer(int kernel);
 
 /* Tensor.matmul(index=) (ferrite/tensor.py:450-460; ferrite/compiler.py:704-706): a mixture of experts' matmul.  W is
@@ -182,6 +184,16 @@ int fb_decode_attention_packed(int cache_fmt, const void* q, int64_t T, int64_t 
                                int64_t cache_rows, const int32_t* base, const int32_t* place, int64_t max_keys, int window, void* out,
                                int64_t ld_o, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same attention for a chunk of ONE sequence's prompt (models/llama.py:498-504, forward over a prompt's tokens at
+ * once): T tokens at places[t], their keys and values already in the cache rows first_row + place, each token seeing
+ * the sequence's keys 0 .. place[t].  A query head's tokens are taken 16 to a CTA, so a key row is read once per 16
+ * tokens of a head.  cache_fmt: FB_BF16 (cache as fb_decode_attention takes it) or FB_BFP8 / FB_BFP4 (as
+ * fb_decode_attention_packed; first_row a multiple of 64).  max_keys: an upper bound of place[t] + 1. */
+size_t fb_prefill_attention_workspace_bytes(int64_t T, int H, int hd, int64_t max_keys);
+int fb_prefill_attention(int cache_fmt, const void* q, int64_t T, int64_t ld_q, int H, int KV, int hd, const void* cache, int64_t cache_rows,
+                         int64_t cache_head_stride, int64_t first_row, const int32_t* places, int64_t max_keys, int window, void* out,
+                         int64_t ld_o, void* workspace, size_t workspace_bytes, void* stream);
+
 /* fb_decode_attention for callers that cannot provide a workspace and must not have one allocated for them (a
  * process whose own pool owns all device memory, a binding with no way to hold a scratch buffer).  It has no
  * counterpart in the reference.  The partial sums of the key splits go into an array built into the library
@@ -231,6 +243,13 @@ int fb_topk(int dtype, const void* x, int64_t rows, int64_t cols, int64_t ldx, i
  * a mixture spread over several GPUs lists only those, numbered from 0, and ignores the picks of other ranks' experts. */
 int fb_touched(const int32_t* ids, const void* weights_bf16, int64_t rows, int k, int n, int first, int32_t* experts, void* out_bf16,
                void* stream);
+
+/* Tensor.group (ferrite/tensor.py:389-402, ferrite/compiler.py:1842-1896): a mixture's tokens grouped by expert, from
+ * int32 choices [rows, k] (values below n; others are left out).  With t = ceil(rows*k / 32) + min(n, rows*k) tiles of
+ * 32 slots and rp = rows rounded up to 32:  order[32 t]: the row each slot holds (0 for none), each value's choices a
+ * run of whole tiles, in the choices' own order;  tiles[t]: each tile's value (n past those used: "none" to a matmul
+ * that picks by them);  places[k * rp]: run j holds, for each row, the slot of its choice j.  One kernel. */
+int fb_group(const int32_t* ids, int64_t rows, int k, int n, int32_t* order, int32_t* tiles, int32_t* places, void* stream);
 
 /* ---- the general operator surface (ferrite/tensor.py:292-372, 443-485), for expressions that are not one of the
  * fused kernels above.  Strides are in elements for (batch, row, col); a stride of 0 broadcasts.  *_host arguments

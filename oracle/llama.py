@@ -261,6 +261,30 @@ def touched(ids, weights, n):
     return np.array(listed, np.int32).reshape(slots, 1), out
 
 
+def group(ids, n):
+    """What Tensor.group gives (ferrite/tensor.py:389-402), after the one-worker kernel that computes it on the chip
+    (ferrite/compiler.py:1842-1896): each value's choices counted, its run of slots starting where the runs of the values
+    before it end, each rounded up to whole tiles of 32, each choice taking the next slot of its value's run in the
+    choices' own order.  (order [32 t], tiles [t], places [k rp]) as int32 arrays."""
+    ids = np.asarray(ids)
+    rows, k = ids.shape
+    t, rp = -(-rows * k // 32) + min(n, rows * k), -(-rows // 32) * 32
+    fill = np.bincount(ids.ravel(), minlength=n)[:n].astype(np.int64)
+    order, tiles, places = np.zeros(32 * t, np.int32), np.full(t, n, np.int32), np.zeros(k * rp, np.int32)
+    s = 0
+    for e in range(n):
+        count, fill[e] = fill[e], s
+        end = s + -(-count // 32) * 32
+        tiles[s // 32:end // 32] = e
+        s = end
+    for r in range(rows):
+        for j in range(k):
+            s = fill[ids[r, j]]
+            fill[ids[r, j]] += 1
+            order[s], places[j * rp + r] = r, s
+    return order, tiles, places
+
+
 def block(w, prefix):
     """The weights named prefix..., by the rest of their names (models/gpt2.py:70)."""
     return {k[len(prefix):]: v for k, v in w.items() if k.startswith(prefix)}

@@ -186,7 +186,7 @@ def make_moe():
          "experts.down": bf(rng.normal(0, 0.1, (16, 64, 64)))}
     out |= {k: gpt2.bf16_bits(v) for k, v in w.items()}
     rc, oc = llama.model(dim=64, k=4), ollama.model(dim=64, k=4)
-    for n in (1, 3, 8, 40):
+    for n in (1, 3, 8, 40, 160):  # (160: more than a decode step's tokens, the grouped form on the device, test_sim.py:1524)
         h, live = bf(rng.normal(0, 1, (n, 64))), np.float32(np.arange(n) != 1).reshape(n, 1)
         want = llama.moe(h, w, rc, live=live)
         assert np.allclose(want, ollama.moe(h, w, oc, live=live), rtol=1e-12, atol=1e-12)

@@ -133,3 +133,32 @@ def test_misuse_is_refused(cuda):
         ops.linear(x, w, epilogue="swiglu")  # 48 columns do not pair up in runs of 16
     with pytest.raises(AssertionError):
         ops.linear(x, w, epilogue="residual")  # no residual given
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("M,K,N,norm,epilogue", [(1, 512, 256, False, "none"), (8, 4096, 6144, True, "none"), (32, 4096, 4096, False, "residual"),
+                                                 (32, 4096, 14336, True, "swiglu"), (17, 512, 1088, False, "none"), (128, 2048, 4096, True, "swiglu"),
+                                                 (48, 1088, 384, False, "residual"), (32, 14336, 512, False, "residual")])
+def test_persistent_kernel(cuda, prefer, fmt, M, K, N, norm, epilogue):
+    # the tcgen05 path as one persistent CTA per SM: runs that are a tail of one tile, whole tiles and a head of another,
+    # tiles shared by up to eight CTAs and summed through the workspace in CTA order (so twice the same bits), a tile
+    # whose second column group does not exist (N = 1088), K that ends inside a step (1088) - against exact products
+    rng = np.random.default_rng(M + K + N)
+    x, wq, tx, packed = case(rng, M, K, N, fmt, cuda)
+    g = bfp.bf16_round(rng.normal(1, 0.1, (1, K)).astype(np.float32)) if norm else None
+    r = bfp.bf16_round(rng.normal(0, 1, (M, N)).astype(np.float32)) if epilogue == "residual" else None
+    h = llama.rms(x.astype(np.float64), g, 1e-5) if norm else x.astype(np.float64)
+    want = h @ wq
+    if epilogue == "swiglu":
+        want = llama.glu(want[:, :N // 2], want[:, N // 2:])
+    if epilogue == "residual":
+        want = want + r
+    kw = dict(out_dtype="fp32", norm_w=to_bf16_tensor(g, cuda) if norm else None, eps=1e-5, epilogue=epilogue,
+              residual=to_bf16_tensor(r, cuda) if r is not None else None)
+    prefer("PERSISTENT")
+    got = ops.linear(tx, packed, **kw)
+    again = ops.linear(tx, packed, **kw)
+    assert torch.equal(got, again), "shared tiles are added in a fixed order"
+    assert rel_err(to_numpy(got), want) < (4e-3 if norm else 2e-5)
+    from ferrite_b200._lib import lib
+    assert lib().fb_status_word() == 0, "no wait gave up"

@@ -123,7 +123,7 @@ def test_moe_block(rt, fmt):
     t = {k: Tensor.of(rt, v.tolist()) for k, v in w.items()}
     t |= {k: t[k].cast(fmt).realize() for k in ("experts.gate_up", "experts.down")}
     c, oc = llama.model(dim=64, k=4), ollama.model(dim=64, k=4)
-    for n in (1, 3, 8, 40):
+    for n in (1, 3, 8, 40, 160):  # (160: the grouped form, each expert's tokens in whole tiles, Tensor.group)
         h, live = bf(rng.normal(0, 1, (n, 64))), np.float32(np.arange(n) != 1).reshape(n, 1)
         got = llama.moe(Tensor.of(rt, h.tolist()), t, c, live=Tensor.of(rt, live.tolist())).realize().numpy()[0]
         want = ollama.moe(h, wq, oc, live=live)

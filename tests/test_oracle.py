@@ -52,7 +52,7 @@ def test_moe_matches_reference_vectors():
     g = golden("moe.npz")
     w = {k: bfp.bf16_floats(g[k]) for k in ("router", "experts.gate_up", "experts.down")}
     c = llama.model(dim=64, k=4)
-    for n in (1, 3, 8, 40):
+    for n in (1, 3, 8, 40, 160):
         h, live = bfp.bf16_floats(g[f"h{n}"]), np.float32(np.arange(n) != 1).reshape(n, 1)
         assert np.allclose(llama.moe(h, w, c, live=live), g[f"y{n}"], rtol=1e-12, atol=1e-12)
 
@@ -169,3 +169,13 @@ def test_experts_by_expert_is_experts():
     want = llama.moe(h, w, c)
     c.by_expert = True
     assert np.allclose(llama.moe(h, w, c), want, rtol=1e-10, atol=1e-12)
+
+
+def test_group_known_answer():
+    # three rows choosing two of four values: value 0 once, 1 twice, 3 three times; runs of whole tiles of 32 in value order
+    order, tiles, places = llama.group(np.array([[3, 1], [0, 3], [1, 3]]), 4)
+    t, rp = -(-6 // 32) + 4, 32
+    assert len(order) == 32 * t and len(tiles) == t and len(places) == 2 * rp
+    assert tiles.tolist() == [0, 1, 3, 4, 4], "value 2 is picked by nobody and takes no tile; 4 marks the tiles past those used"
+    assert order[0] == 1 and order[32:34].tolist() == [0, 2] and order[64:67].tolist() == [0, 1, 2]
+    assert places[:3].tolist() == [64, 0, 33] and places[rp:rp + 3].tolist() == [32, 65, 66]

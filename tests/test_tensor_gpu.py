@@ -149,6 +149,29 @@ def test_topk_and_touched(rt):
     assert np.array_equal(weights.numpy(), ow)
 
 
+def test_group(rt):
+    # Tensor.group against the restated counting sort, slot for slot: the reference's own case (40 rows, top-4 of 16,
+    # test/test_sim.py:1506), one value taking every choice, values nobody picks, a prompt-sized case
+    from ferrite_b200.tensor import Tensor
+    rng = np.random.default_rng(47)
+    x = bf16(rng.normal(0, 1, (40, 16)))
+    cases = [(Tensor.of(rt, x.tolist()).topk(4)[1].numpy()[0], 16), (np.zeros((5, 2), np.int64), 4), (rng.integers(3, 5, (70, 1)), 8),
+             (rng.integers(0, 128, (2048, 8)), 128), (np.array([[1]]), 2)]
+    for ids, n in cases:
+        order, tiles, places = Tensor.of(rt, ids.tolist(), "int32").group(n)
+        want = ollama.group(ids, n)
+        assert order.shape == (1, 1, len(want[0])) and tiles.shape == (1, len(want[1]), 1) and places.shape == (1, 1, len(want[2]))
+        for got, w in zip((order, tiles, places), want):
+            assert np.array_equal(got.numpy().reshape(-1), w), (ids.shape, n)
+        # what it is for: each expert's rows are whole tiles, and places lead every choice back to its row
+        rows, k = ids.shape
+        rp, o, pl, tl = -(-rows // 32) * 32, want[0], want[2], want[1]
+        for r in range(rows):
+            for j in range(k):
+                s = pl[j * rp + r]
+                assert o[s] == r and tl[s // 32] == ids[r, j]
+
+
 def test_attend(rt):
     # the shape of the reference's test_attend (test/test_sim.py:641-680): several rows of queries each with its place,
     # a key head serving two query heads (a repeat read in place), one column of places for all, a sliding window

@@ -671,7 +671,7 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
     }
   } else {
     // ---- the epilogue warps: warp 20 + q reads quarter q of the TMEM lanes (tile rows 32q .. 32q + 31), all tokens
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int qd = warp - WARP_EPI, row = 32 * qd + lane, etid = tid - WARP_EPI * 32;
     griddep_wait();  // the row scales, the residual and the arrival words are the work of kernels before this one
     for (int t = etid; t < 128; t += 128) tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
@@ -710,54 +710,64 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
       const bool even = g.k_steps > 1 || !(g.i_first & 1), odd = g.k_steps > 1 || (g.i_first & 1);  // which accumulators hold steps
       const uint32_t acc = tmem + ((uint32_t)(32 * qd) << 16) + 2 * pair * nt;
       float* mine = p.partials + (size_t)blockIdx.x * nt * TILE_N;
-      // 16 tokens at a time, and within them every load of a kind issued before the first is used: an epilogue is a
-      // few trips to memory (residual, the other CTAs' partial sums), not one per eight tokens
-      for (int c0 = 0; c0 < nt && c0 < a.M; c0 += 16) {
-        float v[16], res[16];
+      // 8 tokens at a time (the epilogue warps have few registers), every load of a kind issued before the first is
+      // used: a pass is one trip to tensor memory, one to the residual, and one per two CTAs whose sums are added
+      for (int c0 = 0; c0 < nt && c0 < a.M; c0 += 8) {
+        float v[8], res[8];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
+        for (int e = 0; e < 8; ++e) {
           const int t = c0 + e;
           res[e] = !tail && live && t < a.M && a.epilogue == FB_EPI_RESIDUAL
                        ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[t * a.ldr + n]) : 0.f;
         }
-#pragma unroll
-        for (int cb = 0; cb < 16; cb += 8) {  // (nt is a multiple of 16)
-          if (even) tmem_ld8(acc + c0 + cb, v + cb);
+        {
+          float w[8];
+          if (even) tmem_ld8_nowait(acc + c0, v);
+          if (odd) tmem_ld8_nowait(acc + nt + c0, w);
+          tmem_ld_wait();
           if (odd) {
-            float w[8];
-            tmem_ld8(acc + nt + c0 + cb, w);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[cb + e] = even ? v[cb + e] + w[e] : w[e];
+            for (int e = 0; e < 8; ++e) v[e] = even ? v[e] + w[e] : w[e];
           }
         }
         if (tail) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
+          for (int e = 0; e < 8; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
           continue;
         }
-        for (int o = 0; o < others; ++o) {  // the rest of the tile, in CTA order
+        for (int o = 0; o < others; o += 2) {  // the rest of the tile, added in CTA order; two CTAs' loads in flight together
           const float* theirs = p.partials + (size_t)(blockIdx.x + 1 + o) * nt * TILE_N + (size_t)c0 * TILE_N + row;
-          float w[16];
+          float w[2][8];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) w[e] = c0 + e < a.M ? __ldcg(theirs + e * TILE_N) : 0.f;
+          for (int b = 0; b < 2; ++b)
 #pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] += w[e];
+            for (int e = 0; e < 8; ++e) w[b][e] = o + b < others && c0 + e < a.M ? __ldcg(theirs + (size_t)b * nt * TILE_N + e * TILE_N) : 0.f;
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += w[b][e];
+        }
+        // (the eight tokens side by side, step by step: eight independent chains instead of one eight times as long)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] *= tok_rstd[c0 + e];
+        if (swiglu) {
+          float up[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) up[e] = __shfl_down_sync(0xffffffffu, v[e], 16);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * up[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += res[e];
         }
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int t = c0 + e;  // (the same for the whole warp)
-          if (t >= a.M) break;
-          float val = v[e] * tok_rstd[t];
-          if (swiglu) {
-            const float up = __shfl_down_sync(0xffffffffu, val, 16);
-            val = val / (1.f + __expf(-val)) * up;
-          } else {
-            val += res[e];
+        for (int e = 0; e < 8; ++e) {
+          const int t = c0 + e;
+          if (t < a.M && live) {
+            const int64_t at = t * a.ldo + n;
+            if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = v[e];
+            else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(v[e]);
           }
-          if (!live) continue;
-          const int64_t at = t * a.ldo + n;
-          if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = val;
-          else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(val);
         }
       }
       tc_fence_before();

@@ -68,6 +68,11 @@ def upload(rt, weights, prec=None):
     (models/llama.py:628-640).  qk_norm / qk_on arrive as the reference stacks them ([heads, 1, hd])."""
     t = {}
     for name, w in weights.items():
+        f = weight_format(name, prec)
+        if callable(getattr(w, "device", None)):  # a checkpoint's Weight (ferrite_b200/checkpoint.py): made on the device, piece by piece
+            x = w.device(rt)
+            t[name] = x.cast(f).realize() if f != "bf16" else x
+            continue
         a = np.asarray(w, np.float32)
         a = a.reshape((1,) * (3 - a.ndim) + a.shape) if a.ndim <= 3 else a
         x = Tensor.of(rt, a)

@@ -452,9 +452,11 @@ class Tensor:
         # a row of `parts` parts is `parts` rows of one part each: one launch for all of them
         check(lib().fb_topk(_lib.DTYPES[x.dtype], x.buf.data_ptr(), x.batch * x.rows * parts, cols, cols, k, ops._ptr(labels.buf) if labels is not None else None,
                             values.buf.data_ptr(), ids.buf.data_ptr(), None, k, ops._stream()))
-        if parts > 1:
-            offs = Tensor.of(self.rt, [[p * cols for p in range(parts) for _ in range(k)]], "int32")
-            ids = (ids + offs).realize()
+        if parts > 1:  # (the parts' first columns: a constant, uploaded once - a recorded step meets it again)
+            key = ("topk parts", parts, cols, k)
+            if key not in self.rt.numbers:
+                self.rt.numbers[key] = Tensor.of(self.rt, [[p * cols for p in range(parts) for _ in range(k)]], "int32")
+            ids = (ids + self.rt.numbers[key]).realize()
         self.rt.launched("topk", 1)
         return values, ids
 

@@ -22,3 +22,29 @@ def test_heads(cuda, vocab):
     assert np.array_equal(ids.numpy()[0], want_ids) and np.array_equal(values.numpy()[0], want_values)
     assert np.allclose(lse.numpy()[0], want_lse, rtol=2e-6, atol=0), (lse.numpy()[0].ravel(), want_lse.ravel())
     assert np.array_equal(serve.heads(logits, k=1)[1].numpy()[0][:, 0], want_ids[:, 0])  # each row's best alone
+
+
+def test_engine_on_the_device_decodes_what_the_oracle_engine_decodes(cuda):
+    # five requests through two slots: prompts in chunks (the prefill-shaped attention over a slot's own rows), a shared
+    # beginning found in a slot, one recorded step for a token of every slot with only the heads read back - the tokens
+    # are those of the same engine driven by the numpy oracle (tests/test_engine.py), greedy
+    from ferrite_b200 import llama, serve
+    from ferrite_b200.tensor import Runtime
+    from test_engine import OracleBackend
+    from test_oracle import MODELS, golden_model
+    rt, name = Runtime(0), "dense_bfp8"
+    c, raw, _, _ = golden_model(name)
+    t = llama.upload(rt, raw, llama.precision(c, MODELS[name][1]))
+    rng = np.random.default_rng(5)
+    system = rng.integers(0, 512, 9).tolist()
+    prompts = [system + [3, 4], rng.integers(0, 512, 5).tolist(), system + [8], rng.integers(0, 512, 12).tolist(), system + [3, 4, 5]]
+    make = lambda: [serve.Request(p, max_tokens=5 + i) for i, p in enumerate(prompts)]
+    want = serve.Engine(OracleBackend(name, 2, 64), slots=2, places=64, chunk=4).run(make())
+    engine = serve.Engine(serve.DeviceBackend(rt, t, c, slots=2, places=64), slots=2, places=64, chunk=4)
+    got = engine.run(make())
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert g.made == w.made and g.cached == w.cached, (i, g.made, w.made)
+    assert got[2].cached >= len(system)
+    # a draw at a temperature from the device's head: the same seed gives the same tokens as from the oracle's head
+    sampled = lambda backend: serve.Engine(backend, slots=2, places=64, chunk=8).run([serve.Request(prompts[1], max_tokens=6, temperature=0.7, top_k=8, seed=1)])[0].made
+    assert sampled(serve.DeviceBackend(rt, t, c, slots=2, places=64)) == sampled(OracleBackend(name, 2, 64))

@@ -56,6 +56,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="fewer blocks than the model has (a smoke run; the JSON line says so)")
     ap.add_argument("--impl", default="ferrite_b200", choices=["ferrite_b200", "reference"])
     ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"], help="several GPUs: how the ranks' partial sums are added")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "ep"],
+                    help="several GPUs: tp = heads / MLP columns / experts sharded, every rank decodes every sequence, all-reduce after o_proj and "
+                         "the MLP; ep (mixtures) = experts AND sequences shared out, whole attention on every rank, tokens to their experts by all-to-all")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "bfp8", "bfp4"], help="the KV cache's format (BASELINE.json's configs keep it in bf16)")
     ap.add_argument("--sweep", type=int, default=1, help="0: leave the isolated matmul sweep out of the line (a profiling run)")
     ap.add_argument("--attend", default="", help="T,H,KV,hd,context[,calls]: only the decode attention, e.g. 32,32,8,128,2048,6")
@@ -107,8 +110,9 @@ def linear_bytes(c, sequences, fmt_bytes=1.0625, expert_bytes=None):
     shapes = [(c.dim, (c.heads + 2 * c.kv) * hd, (c.heads + 2 * c.kv) * hd, fmt_bytes), (c.heads * hd, c.dim, c.dim, fmt_bytes)]
     launches = 2
     if getattr(c, "experts", 0):
-        tp = getattr(c, "tp", None)  # expert parallel: a rank reads its share of the touched experts
-        touched = c.experts * (1 - (1 - c.k / c.experts) ** max(sequences, 1)) / (tp.world if tp else 1)
+        tp = getattr(c, "tp", None) or getattr(c, "ep", None)  # expert parallel: a rank reads its share of the touched experts
+        everyone = sequences * (tp.world if getattr(c, "ep", None) else 1)  # (c.ep: the other ranks' sequences pick this rank's experts too)
+        touched = c.experts * (1 - (1 - c.k / c.experts) ** max(everyone, 1)) / (tp.world if tp else 1)
         eb = expert_bytes or fmt_bytes
         shapes += [(c.dim, c.experts, c.experts, 2.0), (c.dim, touched * 2 * c.moe, touched * c.moe, eb), (touched * c.moe, c.dim, c.dim, eb)]
         launches += 3
@@ -145,11 +149,15 @@ def run_ferrite(args):
     full = llama.model(**wl["model"], places=wl["context"] + args.steps + args.warmup + 64)
     if args.layers:
         full.layers = args.layers
-    c = llama.tensor_parallel(full, rank, world, dist.group.WORLD) if world > 1 else full
+    ep = world > 1 and args.parallel == "ep"
+    assert not ep or (getattr(full, "experts", 0) and wl["sequences"] % world == 0), "--parallel ep: a mixture, its sequences shared out evenly"
+    c = llama.expert_parallel(full, rank, world, dist.group.WORLD) if ep else llama.tensor_parallel(full, rank, world, dist.group.WORLD) if world > 1 else full
     if world == 1:
         c.vocab_shard = full.vocab
     reduction = "none"
-    if world > 1:
+    if ep:
+        reduction = "none (two all-to-alls a block: tokens to their experts' ranks and back)"
+    elif world > 1:
         reduction = "nccl all-reduce + add"
         if args.reduce == "peer":
             why = ""
@@ -166,12 +174,14 @@ def run_ferrite(args):
                 reduction += f" (peer memory unavailable on some rank{': ' + why if why else ''})"
     prec = llama.precision(full, wl["mode"])
     w = llama.random_weights(rt, c, prec, seed=0, full=full)
-    S, ctx = wl["sequences"], wl["context"]
+    S_all, ctx = wl["sequences"], wl["context"]
+    S = S_all // world if ep else S_all  # the sequences this rank decodes
     part = ctx + args.steps + args.warmup + 64
     part += -part % 64
     rng = np.random.default_rng(0)
     # where each sequence stands: all at `context`, or (a serving mix) contexts drawn uniformly, seeded
-    ctxs = [int(v) for v in rng.integers(wl["ragged"][0], wl["ragged"][1] + 1, S)] if wl.get("ragged") else [ctx] * S
+    ctxs = [int(v) for v in rng.integers(wl["ragged"][0], wl["ragged"][1] + 1, S_all)] if wl.get("ragged") else [ctx] * S_all
+    ctxs = ctxs[rank * S:(rank + 1) * S] if ep else ctxs
     moe = bool(getattr(full, "experts", 0))
     expert_bytes = 0.5625 if wl["mode"] == "experts" else None
     hd = llama.head(full)
@@ -189,7 +199,8 @@ def run_ferrite(args):
 
     step = jit(step_fn)
     on = lambda row: Tensor.of(rt, [row], "int32")
-    ids0 = [int(v) for v in rng.integers(0, full.vocab, S)]
+    ids0 = [int(v) for v in rng.integers(0, full.vocab, S_all)]
+    ids0 = ids0[rank * S:(rank + 1) * S] if ep else ids0
     place = 0  # steps taken so far: sequence u stands at ctxs[u] + place
     at = lambda: [v + place for v in ctxs]
     # the first two calls plan and record; they are part of the warm-up
@@ -299,12 +310,13 @@ def run_ferrite(args):
         lin_bytes, lin_launches, lin_ms = whole, int(per_step or 1), ms / args.steps
     achieved = lin_bytes / (lin_ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tokens/s", "value": S * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": "decode tokens/s", "value": S_all * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": f"tp{world}" + (f" (attention heads) + ep{world} (experts), all-reduce after o_proj and after the experts" if moe and world > 1 else ""), "reduction": reduction, "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
+        "config": {"workload": wl["name"], "layers": full.layers, "parallelism": (f"dp{world} (sequences, whole attention) + ep{world} (experts), all-to-all dispatch and return" if ep else
+                                                                             f"tp{world}" + (f" (attention heads) + ep{world} (experts), all-reduce after o_proj and after the experts" if moe and world > 1 else "")), "reduction": reduction, "l2": "inputs larger than L2 (every step streams all weights and KV rows)",
                    "weights": "random N(0, 0.02) quantised on the device", "kv": "N(0, 1) %s standing in for the prompts' prefill" % args.kv},
-        "e2e": {"value": S * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S, "d2h_bytes_per_step": 4 * S, "steps": e2e_steps},
+        "e2e": {"value": S_all * e2e_steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * S_all, "d2h_bytes_per_step": 4 * S_all, "steps": e2e_steps},
         "gpu_launches": int(per_step or 0) * args.steps,
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": ("the whole decode step (indexed block-float matmuls + decode attention), %d tokens" if moe else
@@ -416,59 +428,89 @@ def matmul_sweep(device, peak_gbs, calls=200):
 
 
 def cpu_sample(args, seconds):
-    """One decode step of ONE block plus the output layer of the workload, by the numpy restatement of the reference's
-    CPU path (oracle/), timed; scaled to the model's block count.  Weights are quantised by the C restatement."""
+    """One decode step of ONE block plus the output layer of the workload on this box's host cores, timed, and scaled to
+    the model's block count.  It runs the reference's OWN numpy code (models/llama.py: around, layer, rms - the numpy
+    branch its `fns` picks) when oracle/_ref holds it (oracle/make_ref.py put it there from a checkout; kind
+    "reference"), else the restatement under oracle/ (kind "port").  Weights are quantised by the C restatement."""
     from oracle import build as obuild
     from oracle import llama as ollama
+    from oracle import make_ref
+    ref = make_ref.modules()
     wl = WORKLOADS[args.workload]
-    c = ollama.model(**{k: v for k, v in wl["model"].items() if k != "tied"}, places=wl["context"] + 64)
-    layers = args.layers or c.layers
-    c.layers = 1
+    fields = {k: v for k, v in wl["model"].items() if k != "tied"} | dict(places=wl["context"] + 64)
+    layers = args.layers or fields["layers"]
+    oc = ollama.model(**fields | dict(layers=1))
+    c = ref[0].model(**{k: v for k, v in fields.items() if k != "qk_norm"} | dict(layers=1)) if ref else oc
     S, ctx = wl["sequences"], wl["context"]
     rng = np.random.default_rng(0)
     ctxs = [int(v) for v in rng.integers(wl["ragged"][0], wl["ragged"][1] + 1, S)] if wl.get("ragged") else [ctx] * S
-    hd, nh = ollama.head(c), c.heads + 2 * c.kv
+    hd, nh = ollama.head(oc), oc.heads + 2 * oc.kv
     fmt = "bfp8" if wl["mode"] == "experts" else wl["mode"]
     q = lambda *shape, f=fmt: obuild.bfp_values(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02), f)
-    w = {"layers.0.input_layernorm": np.ones((1, c.dim), np.float32), "layers.0.post_attention_layernorm": np.ones((1, c.dim), np.float32),
-         "layers.0.qkv_proj": q(c.dim, nh * hd), "layers.0.o_proj": q(c.heads * hd, c.dim), "norm": np.ones((1, c.dim), np.float32)}
-    if getattr(c, "experts", 0):
+    w = {"layers.0.input_layernorm": np.ones((1, oc.dim), np.float32), "layers.0.post_attention_layernorm": np.ones((1, oc.dim), np.float32),
+         "layers.0.qkv_proj": q(oc.dim, nh * hd), "layers.0.o_proj": q(oc.heads * hd, oc.dim), "norm": np.ones((1, oc.dim), np.float32)}
+    if getattr(oc, "experts", 0):
         ef = "bfp4" if wl["mode"] == "experts" else fmt
-        w["layers.0.router"] = (rng.standard_normal((c.dim, c.experts), dtype=np.float32) * np.float32(0.02))
-        w["layers.0.experts.gate_up"] = np.stack([q(c.dim, 2 * c.moe, f=ef) for _ in range(c.experts)])
-        w["layers.0.experts.down"] = np.stack([q(c.moe, c.dim, f=ef) for _ in range(c.experts)])
+        w["layers.0.router"] = (rng.standard_normal((oc.dim, oc.experts), dtype=np.float32) * np.float32(0.02))
+        w["layers.0.experts.gate_up"] = np.stack([q(oc.dim, 2 * oc.moe, f=ef) for _ in range(oc.experts)])
+        w["layers.0.experts.down"] = np.stack([q(oc.moe, oc.dim, f=ef) for _ in range(oc.experts)])
         if wl["model"].get("qk_norm"):
             w["layers.0.qk_norm"] = np.ones((nh, 1, hd), np.float32)
-            w["layers.0.qk_on"] = np.array([1.0] * (c.heads + c.kv) + [0.0] * c.kv, np.float32).reshape(nh, 1, 1)
+            w["layers.0.qk_on"] = np.array([1.0] * (oc.heads + oc.kv) + [0.0] * oc.kv, np.float32).reshape(nh, 1, 1)
     else:
-        w["layers.0.gate_up_proj"], w["layers.0.down_proj"] = q(c.dim, 2 * c.ffn), q(c.ffn, c.dim)
-    w["embed"] = (rng.standard_normal((c.vocab, c.dim), dtype=np.float32) * np.float32(0.02))
+        w["layers.0.gate_up_proj"], w["layers.0.down_proj"] = q(oc.dim, 2 * oc.ffn), q(oc.ffn, oc.dim)
+    w["embed"] = (rng.standard_normal((oc.vocab, oc.dim), dtype=np.float32) * np.float32(0.02))
     w["embed.T"] = obuild.bfp_values(np.ascontiguousarray(w["embed"].T), fmt)
-    w["cos"], w["sin"] = ollama.rotary(c, c.places)
+    if ref:
+        w["cos"], w["sin"], w["turn"] = ref[0].rotary(c, c.places)
+    else:
+        w["cos"], w["sin"] = ollama.rotary(oc, oc.places)
     part = ctx + 64
-    caches = ollama.kv_cache(c, S * part)  # np.zeros: float64, as the reference's
+    caches = [np.zeros((2 * oc.kv, S * part, hd))]  # np.zeros: float64, as the reference's kv_cache(c, size, np.zeros)
     caches[0][:, :, :] = rng.standard_normal(caches[0].shape)
-    ids = [int(v) for v in rng.integers(0, c.vocab, S)]
+    ids = [int(v) for v in rng.integers(0, oc.vocab, S)]
     slots = S if S > 1 else None
+    threads = blas_threads()
     times, place = [], 0
     start = time.perf_counter()
     while not times or (time.perf_counter() - start < seconds and len(times) < 16):
         t0 = time.perf_counter()
         x = w["embed"][ids]
-        rows, cos, sin, mask, live = ollama.around(w, c, [v + place for v in ctxs] if slots else [ctx + place], S * part if slots else part, slots)
+        places, size = ([v + place for v in ctxs] if slots else [ctx + place]), (S * part if slots else part)
+        if ref:
+            rows, rotary, mask, _, live = ref[0].around(w, c, places, size, slots)
+        else:
+            rows, cos, sin, mask, live = ollama.around(w, oc, places, size, slots)
         t_in = time.perf_counter()
-        x = ollama.layer(x, ollama.block(w, "layers.0."), c, cos, sin, mask, caches[0], rows, live, slots)
+        if ref:
+            x = ref[0].layer(x, ref[1].block(w, "layers.0."), c, rotary, mask, caches[0], rows, 0, False, live, None, slots)
+        else:
+            x = ollama.layer(x, ollama.block(w, "layers.0."), oc, cos, sin, mask, caches[0], rows, live, slots)
         t_layer = time.perf_counter()
-        logits = ollama.rms(x, w["norm"], c.eps) @ w["embed.T"]
+        logits = (ref[0].rms(x, w["norm"], c) if ref else ollama.rms(x, w["norm"], oc.eps)) @ w["embed.T"]
         picks = logits.argmax(-1)
         t_head = time.perf_counter()
         times.append(((t_in - t0) + (t_head - t_layer), t_layer - t_in))
         place += 1
     rest, layer = np.median([t[0] for t in times]), np.median([t[1] for t in times])
     step_seconds = rest + layers * layer
-    return {"value": S / step_seconds, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{len(times)} decode steps of 1 of {layers} blocks plus embedding and output layer in numpy (float32 weights, float64 KV cache as the "
-                      f"reference keeps it); block time x {layers} + the rest", "seconds_per_step_scaled": step_seconds}
+    return {"value": S / step_seconds, "unit": "tokens/s", "cores": os.cpu_count(), "blas_threads": threads, "kind": "reference" if ref else "port",
+            "sample": f"{len(times)} decode steps of 1 of {layers} blocks plus embedding and output layer, "
+                      + ("the reference's own models/llama.py numpy branch" if ref else "the numpy restatement of the reference's CPU path")
+                      + " (float32 weights, float64 KV cache as the reference keeps it); block time x " + f"{layers} + the rest",
+            "seconds_per_step_scaled": step_seconds}
+
+
+def blas_threads():
+    """The threads numpy's BLAS uses (what the CPU legs' matmuls run on), pinned to the host's cores where a launcher
+    set it to one (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers)."""
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+        want = os.cpu_count() or 1
+        threadpool_limits(want)
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:  # noqa: BLE001  (threadpoolctl missing: numpy's default)
+        return None
 
 
 def cpu_baseline(args, sample_seconds):

@@ -128,6 +128,8 @@ def experts(h, p, ids, w, c=None):
     """Expert parallel (c.tp): every rank routes every token (the router is replicated) and holds a run of the experts;
     it lists and runs the touched experts it holds, so its result is a partial sum, reduced over the ranks like a
     row-sharded down_proj's (`added`)."""
+    if getattr(c, "ep", None):
+        return experts_dispatched(h, p, ids, w, c)
     gate_up, down = p["experts.gate_up"], p["experts.down"]
     m, e = down.rows, gate_up.batch
     tp = getattr(c, "tp", None)
@@ -154,6 +156,51 @@ def experts(h, p, ids, w, c=None):
     for term in terms[1:]:
         out = out + term
     return out
+
+
+def experts_dispatched(h, p, ids, w, c):
+    """Expert parallel with the TOKENS shared out too (c.ep, from expert_parallel): every rank decodes its own sequences
+    with the whole attention, holds a run of whole experts, and a token's row travels to the ranks that hold its chosen
+    experts and its results come back: two all-to-alls over NVLink a block, no all-reduce.  Shapes are fixed, so the step
+    records as a CUDA graph: a rank sends every peer one buffer of tokens x k slots, slot (t, j) filled in the buffer of
+    the rank that owns token t's choice j and marked "none" in the others; a receiver groups the slots it was sent by
+    expert into whole tiles (Tensor.group), runs its experts' SwiGLUs over them, and returns every slot's row in place;
+    the sender picks each choice's row out of its owner's buffer and adds them up by their weights.  The reference
+    drives one chip and has no counterpart (ferrite/runtime.py:304-311); the arithmetic is numpy_experts'
+    (models/llama.py:294-300)."""
+    import torch.distributed as dist
+    ep, rt = c.ep, h.rt
+    gate_up, down = p["experts.gate_up"], p["experts.down"]
+    m, e, R = down.rows, gate_up.batch, ep.world
+    n, k, d = ids.rows, ids.cols, h.cols
+    cap = n * k
+    key = ("dispatch", n, k, R)
+    if key not in rt.numbers:  # constants of the step's shape: each slot's token, each slot's number, the ranks
+        rt.numbers[key] = (Tensor.of(rt, [[t for t in range(n) for _ in range(k)] * R], "int32"),
+                           Tensor.of(rt, [[t * k + j for j in range(k)] for t in range(n)], "int32"),
+                           Tensor.of(rt, [[[r]] for r in range(R)], "int32"))
+    token_of_slot, slot_of, ranks = rt.numbers[key]
+    h, ids, w = h.realize(), ids.realize(), w.bfloat16().realize()
+    owner = ids >= e  # the rank that holds each choice: how many ranks' runs of experts lie at or below it
+    for r in range(2, R):
+        owner = owner + (ids >= r * e)
+    owner = owner.realize() if R > 1 else (ids * 0).realize()
+    here = owner.eq(ranks)  # [R, n, k]: 1 in the buffer of the owner
+    meta = ((ids - owner * e) * here + (1 - here) * e).realize()  # the expert's number on its owner, "none" (e) elsewhere
+    send = h.gather(token_of_slot)  # [R * cap, d]: every buffer holds every slot's token (only the owner's copy is used)
+    recv, rmeta = Tensor(rt, R * cap, d), Tensor(rt, R * cap, 1, dtype="int32")
+    dist.all_to_all_single(recv.buf.view(R * cap, d), send.buf.view(R * cap, d), group=ep.group)
+    dist.all_to_all_single(rmeta.buf.view(R * cap), meta.buf.view(R * cap), group=ep.group)
+    rt.launched("all-to-all dispatch")
+    order, picks, places = rmeta.group(e)
+    x = recv.gather(order).split(picks.rows, 1)
+    x = x.matmul(gate_up, index=picks).realize()
+    y = glu(x[:, :, :m], x[:, :, m:]).matmul(down, index=picks).realize().reshape(order.cols, d)
+    back, ret = y.gather(places[:, :, :R * cap]), Tensor(rt, R * cap, d)
+    dist.all_to_all_single(ret.buf.view(R * cap, d), back.buf.view(R * cap, d), group=ep.group)
+    rt.launched("all-to-all return")
+    mine = ret.gather((owner * cap + slot_of).realize().reshape(1, 1, cap)).reshape(n, k, d)  # each choice's row, from its owner's buffer
+    return (mine * w.reshape(n, k, 1)).sum(1).reshape(1, n, d)
 
 
 def layer(x, p, c, rotary, seen, cache, rows, live=None, slots=None):
@@ -200,6 +247,17 @@ def tensor_parallel(c, rank, world, group=None):
     local.head_dim, local.heads, local.kv, local.dim = head(c), c.heads // world, max(c.kv // world, 1), c.dim
     local.ffn, local.vocab_shard = (c.ffn or 0) // world, c.vocab // world
     local.tp = SimpleNamespace(rank=rank, world=world, group=group, peer=None)
+    return local
+
+
+def expert_parallel(c, rank, world, group=None):
+    """c as rank `rank` of `world` holds it when a mixture's experts AND its sequences are shared out: the whole attention
+    and output layer on every rank (each decodes its own sequences), a run of whole experts each, tokens travelling to
+    their experts by all-to-all (experts_dispatched)."""
+    assert (getattr(c, "experts", 0) or 0) % world == 0 and c.experts, "a mixture, every rank holding the same number of whole experts"
+    local = SimpleNamespace(**vars(c))
+    local.ep = SimpleNamespace(rank=rank, world=world, group=group)
+    local.vocab_shard = c.vocab
     return local
 
 
@@ -377,7 +435,8 @@ def random_weights(rt, c, prec=None, seed=0, scale=0.02, full=None):
     keeps its columns or rows, so the ranks together hold exactly the one-GPU model."""
     gen = torch.Generator(device=rt.device).manual_seed(seed)
     full = full or c
-    tp = getattr(c, "tp", None)
+    tp = getattr(c, "tp", None) or getattr(c, "ep", None)
+    only_experts = getattr(c, "tp", None) is None  # (c.ep: the attention and the output layer are whole on every rank)
     r, n = (tp.rank, tp.world) if tp else (0, 1)
     hd, d = head(full), full.dim
     H, KV = full.heads, full.kv
@@ -394,7 +453,7 @@ def random_weights(rt, c, prec=None, seed=0, scale=0.02, full=None):
         return torch.empty(*shape, dtype=torch.float32, device=rt.device).normal_(0, scale, generator=gen).bfloat16()
 
     def mine(name):
-        kept = tp_keep(name, full, r, n) if tp else None
+        kept = tp_keep(name, full, r, n) if tp and (not only_experts or name.endswith(("experts.gate_up", "experts.down"))) else None
         if kept is None:
             return None
         axis, idx = kept

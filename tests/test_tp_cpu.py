@@ -142,3 +142,58 @@ def test_key_heads_shared_by_ranks_when_there_are_fewer_of_them():
         rows = llama.tp_keep("o_proj", full, rank, world)[1]
         total = total + heads_out(x @ wqkv[:, cols], 2, 1) @ wo[rows]
     assert np.allclose(total, want, rtol=1e-10, atol=1e-12)
+
+
+def _dispatch_worker(rank, world, port, result):
+    """The all-to-all dispatch of ferrite_b200.llama.experts_dispatched, its layout restated in numpy over two gloo
+    ranks: each rank routes its OWN tokens, sends every rank a buffer of tokens x k slots (slot (t, j) real in the
+    owner's buffer, "none" elsewhere), runs its experts over what it receives, returns the rows in place, and the sender
+    adds its choices' rows by their weights - against the one-device mixture (oracle.llama.moe) on those tokens."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(3)
+    d, E, F, k, n = 32, 8, 16, 2, 5
+    full = ollama.model(dim=d, experts=E, k=k, moe=F)
+    p = {"router": rng.normal(0, 0.5, (d, E)), "experts.gate_up": rng.normal(0, 0.2, (E, d, 2 * F)), "experts.down": rng.normal(0, 0.2, (E, F, d))}
+    h = np.random.default_rng(10 + rank).normal(0, 1, (n, d))  # this rank's own tokens
+    e = E // world
+    vals, ids = ollama.topk(h @ p["router"], k)
+    w = ollama.softmax(vals)
+    owner, cap = ids // e, n * k
+    send = np.zeros((world, cap, d))
+    meta = np.full((world, cap), e)
+    for t in range(n):
+        for j in range(k):
+            send[:, t * k + j] = h[t]
+            meta[owner[t, j], t * k + j] = ids[t, j] - owner[t, j] * e
+    def exchange(a):  # all-to-all by an all-gather (every rank takes its own slice of everyone's buffers)
+        every = [torch.zeros_like(torch.from_numpy(a)) for _ in range(world)]
+        dist.all_gather(every, torch.from_numpy(a.copy()))
+        return np.stack([x.numpy()[rank] for x in every])
+    recv, rmeta = exchange(send), exchange(meta)
+    back = np.zeros_like(recv)
+    for r in range(world):
+        for s in range(cap):
+            if rmeta[r, s] < e:
+                g = recv[r, s] @ p["experts.gate_up"][rank * e + rmeta[r, s]]
+                back[r, s] = ollama.glu(g[:F], g[F:]) @ p["experts.down"][rank * e + rmeta[r, s]]
+    ret = exchange(back)
+    out = np.stack([sum(w[t, j] * ret[owner[t, j], t * k + j] for j in range(k)) for t in range(n)])
+    ok = torch.tensor([int(np.allclose(out, ollama.moe(h, p, full), rtol=1e-10, atol=1e-12))])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        result.put(bool(ok.item()))
+    dist.destroy_process_group()
+
+
+def test_two_ranks_dispatch_tokens_to_their_experts():
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dispatch_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert result.get(timeout=5)

@@ -63,6 +63,67 @@ def _worker(rank, world, port, result, kind="dense", peer=False):
     os._exit(0)  # (no NCCL teardown: the recorded graphs still hold its kernels)
 
 
+def _ep_worker(rank, world, port, result):
+    """A mixture with its experts AND its sequences shared out (llama.expert_parallel): every rank decodes its own two
+    sequences, tokens reach their experts by all-to-all, and each rank checks its sequences against the one-GPU decoder."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from ferrite_b200 import llama
+    from ferrite_b200.tensor import Runtime, Tensor, jit
+    rt = Runtime(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=rt.device)
+    full = llama.model(**MODELS["mixture"][0])
+    full.vocab_shard = full.vocab
+    prec = llama.precision(full, MODELS["mixture"][1])
+    c = llama.expert_parallel(full, rank, world, dist.group.WORLD)
+    w = llama.random_weights(rt, c, prec, seed=5, full=full, scale=0.05)
+    assert w["layers.0.experts.gate_up"].batch == full.experts // world and w["layers.0.qkv_proj"].cols == (8 + 2 * 4) * 64
+    S, part = 2, 32
+    on = lambda row: Tensor.of(rt, [row], "int32")
+    kv = llama.kv_cache(c, S * part, llama.zeros(rt))
+    step = jit(lambda ids, places: llama.forward(ids, places, w, c, kv, S))
+    w1 = llama.random_weights(rt, full, prec, seed=5, scale=0.05)  # the same model whole, on this GPU
+    kv1 = llama.kv_cache(full, S * part, llama.zeros(rt))
+    step1 = jit(lambda ids, places: llama.forward(ids, places, w1, full, kv1, S))
+    ids, worst = [3 + 100 * rank, 500 + rank], 0.0
+    for i in range(5):  # eager, recorded, replayed; teacher-forced with the whole model's picks
+        got, want = step(on(ids), on([i] * S)).numpy()[0], step1(on(ids), on([i] * S)).numpy()[0]
+        worst = max(worst, float(np.abs(got - want).max() / np.ptp(want)))
+        ids = [int(v) for v in want.argmax(-1)]
+    flag = torch.tensor([worst], device=rt.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        result.put(float(flag.item()))
+        import time
+        time.sleep(1)
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_experts_and_sequences_shared_out_by_all_to_all(cuda, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.kill()
+        p.join(10)
+    assert not stuck and all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert result.get(timeout=5) < 0.02, "every rank's logits within 2 % of the whole model's span"
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("kind,peer", [("dense", False), ("mixture", False), ("dense", True), ("mixture", True)])
 def test_ranks_decode_like_one_gpu(cuda, kind, peer, world):

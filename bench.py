@@ -298,6 +298,23 @@ def run_ferrite(args):
         torch.cuda.synchronize()
         lin_ms = e4.elapsed_time(e5) / reps
 
+    # ---- time to first token (one GPU, a dense model): one sequence's prompt of `context` tokens from place 0 in chunks of
+    # 128 through the same kernels (the matmuls at 128 rows a pass, the prefill-shaped attention), then the greedy pick
+    # (the reference's B3, test/benchmark.py:172-181, times the same call on its side)
+    ttft = None
+    if world == 1 and not moe:
+        prompt = [int(v) for v in rng.integers(0, full.vocab, ctx)]
+        one = llama.kv_cache(c, part, llama.zeros(rt))
+        tries = []
+        for _ in range(2):  # (the first pass also plans and allocates)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            first = llama.next_tokens(llama.prefill(prompt, w, c, one, 128, on), c).numpy()
+            tries.append(time.perf_counter() - t0)
+        ttft = {"ms": 1e3 * tries[-1], "prompt_tokens": ctx, "chunk": 128, "tokens_per_s": ctx / tries[-1],
+                "what": "one sequence's prompt from place 0 to its first token on the host, wall clock, second of two passes"}
+        del one
+
     # max over ranks
     times = torch.tensor([ms, ms_e2e, lin_ms], device=rt.device)
     if world > 1:
@@ -327,6 +344,8 @@ def run_ferrite(args):
                      "launches": lin_launches, "us_per_launch": lin_ms * 1e3 / lin_launches, "bytes_per_launch": lin_bytes / lin_launches},
         "step_roofline": {"algorithmic_bytes_per_gpu": whole, "frac_of_hbm": whole / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }
+    if ttft:
+        line["ttft"] = ttft
     if rank == 0 and world == 1:
         del w, caches, step, mm
         torch.cuda.empty_cache()

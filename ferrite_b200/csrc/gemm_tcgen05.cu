@@ -716,58 +716,46 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
       const bool even = g.k_steps > 1 || !(g.i_first & 1), odd = g.k_steps > 1 || (g.i_first & 1);  // which accumulators hold steps
       const uint32_t acc = tmem + ((uint32_t)(32 * qd) << 16) + 2 * pair * nt;
       float* mine = p.partials + (size_t)blockIdx.x * nt * TILE_N;
-      // 8 tokens at a time (the epilogue warps have few registers), every load of a kind issued before the first is
-      // used: a pass is one trip to tensor memory, one to the residual, and one per two CTAs whose sums are added
-      for (int c0 = 0; c0 < nt && c0 < a.M; c0 += 8) {
-        float v[8], res[8];
+      // 16 tokens at a time (nt is a multiple of 16), one kind of load after another, every load of a kind in flight
+      // before the first is used: a pass is ONE trip to tensor memory, one per CTA whose sums are added, one to the
+      // residual - not one per token, and the arithmetic is sixteen independent chains
+      for (int c0 = 0; c0 < nt && c0 < a.M; c0 += 16) {
+        float v[16], w[16];
+        if (even) tmem_ld16_nowait(acc + c0, v);
+        if (odd) tmem_ld16_nowait(acc + nt + c0, w);
+        tmem_ld_wait();
+        if (odd) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int t = c0 + e;
-          res[e] = !tail && live && t < a.M && a.epilogue == FB_EPI_RESIDUAL
-                       ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[t * a.ldr + n]) : 0.f;
-        }
-        {
-          float w[8];
-          if (even) tmem_ld8_nowait(acc + c0, v);
-          if (odd) tmem_ld8_nowait(acc + nt + c0, w);
-          tmem_ld_wait();
-          if (odd) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = even ? v[e] + w[e] : w[e];
-          }
+          for (int e = 0; e < 16; ++e) v[e] = even ? v[e] + w[e] : w[e];
         }
         if (tail) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
+          for (int e = 0; e < 16; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
           continue;
         }
-        for (int o = 0; o < others; o += 2) {  // the rest of the tile, added in CTA order; two CTAs' loads in flight together
+        for (int o = 0; o < others; ++o) {  // the rest of the tile, added in CTA order
           const float* theirs = p.partials + (size_t)(blockIdx.x + 1 + o) * nt * TILE_N + (size_t)c0 * TILE_N + row;
-          float w[2][8];
 #pragma unroll
-          for (int b = 0; b < 2; ++b)
+          for (int e = 0; e < 16; ++e) w[e] = c0 + e < a.M ? __ldcg(theirs + e * TILE_N) : 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) w[b][e] = o + b < others && c0 + e < a.M ? __ldcg(theirs + (size_t)b * nt * TILE_N + e * TILE_N) : 0.f;
-#pragma unroll
-          for (int b = 0; b < 2; ++b)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += w[b][e];
+          for (int e = 0; e < 16; ++e) v[e] += w[e];
         }
-        // (the eight tokens side by side, step by step: eight independent chains instead of one eight times as long)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] *= tok_rstd[c0 + e];
+        for (int e = 0; e < 16; ++e) v[e] *= tok_rstd[c0 + e];
         if (swiglu) {
-          float up[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) up[e] = __shfl_down_sync(0xffffffffu, v[e], 16);
+          for (int e = 0; e < 16; ++e) w[e] = __shfl_down_sync(0xffffffffu, v[e], 16);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * up[e];
-        } else {
+          for (int e = 0; e < 16; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * w[e];
+        } else if (a.epilogue == FB_EPI_RESIDUAL) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] += res[e];
+          for (int e = 0; e < 16; ++e)
+            w[e] = live && c0 + e < a.M ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[(c0 + e) * a.ldr + n]) : 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] += w[e];
         }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < 16; ++e) {
           const int t = c0 + e;
           if (t < a.M && live) {
             const int64_t at = t * a.ldo + n;

@@ -28,6 +28,8 @@ SIGNATURES = {
     "fb_linear_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fb_linear_prefer": (_i, [_i]),
     "fb_linear": (_i, [_i, _p, _i64, _i64, _i64, _p, _i64, _p, _i, _i64, _p, _f, _i, _p, _i64, _p, _sz, _p]),
+    "fb_linear_chain_parts": (_i, [_i, _i64, _i64, _i64, _i]),
+    "fb_linear_chained": (_i, [_i, _p, _i64, _i64, _i64, _p, _i64, _p, _i, _i64, _f, _i, _p, _i64, _p, _i, _p, _p, _i64, _p, _p, _sz, _p]),
     "fb_linear_indexed": (_i, [_i, _p, _i64, _i64, _i64, _i64, _p, _i64, _i, _p, _i, _i, _p, _i, _i64, _i64, _p, _f, _i, _p, _i64, _p, _p, _sz, _p]),
     "fb_gather_rows": (_i, [_p, _i64, _i64, _p, _i64, _p, _p]),
     "fb_put_rows": (_i, [_p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _i64, _i, _p]),

@@ -51,6 +51,8 @@ struct GemmParams {
   int splits, steps_per_split, steps_total;  // K in steps of 128 rows
   int x_slots, a_slots;
   const float* rstd;  // [M] row scales of the RMSNorm prologue, or null
+  const float* sumsq_in;  // or: [sumsq_parts, M] partial sums of squares of the rows x was normalised from (LinearArgs)
+  int sumsq_parts;
   // a mixture of experts' matmul (Tensor.matmul(index=), ferrite/tensor.py:450-460): W is a batch of n_experts packed
   // matrices expert_bytes apart and index[slot] picks one per slot (n_experts or more: none, zeros).
   //   mode 1: one result per slot (grid z): out + slot * out_slot_stride, x rows from slot * x_slot_rows on
@@ -169,7 +171,13 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   if (warp == WARP_X && lane >= 16) {  // the epilogue's per-token factors, fetched while the matmul runs
     griddep_wait();
     for (int t = lane - 16; t < nt; t += 16) {
-      tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
+      float rs = p.rstd && t < a.M ? p.rstd[t] : 1.f;
+      if (p.sumsq_in && t < a.M) {  // the matmul before this one left the rows' sums of squares, a part per CTA: added in part order
+        float ss = 0.f;
+        for (int q = 0; q < p.sumsq_parts; ++q) ss += p.sumsq_in[(int64_t)q * a.M + t];
+        rs = rsqrtf(ss / (float)K + a.eps);
+      }
+      tok_rstd[t] = rs;
       tok_scale[t] = p.row_scale && t < a.M ? bf16_bits_to_float(p.row_scale[(int64_t)zslot * a.M + t]) : 1.f;
     }
   } else if (warp == WARP_X && lane <= PREFETCH) {
@@ -438,6 +446,28 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem, p.tmem_cols);
+  }
+  // ---- the next matmul's RMSNorm, handed on (LinearArgs::next_norm_w): over the columns this CTA has just written - a
+  // slice of the tile's with a K split - xn = bf16(out * g) and each token's sum of out^2, one part per CTA.  The values
+  // are read back as stored (bf16), so xn and the sums are those a separate pass over `out` would compute; the sum over
+  // a part's columns is a warp's butterfly, the same every run.
+  if (a.xn_out != nullptr && worker) {
+    const int n0 = TILE_N * tile + (splits > 1 ? split * rows_per : 0);
+    const int own = min(splits > 1 ? min(rows_per, TILE_N - split * rows_per) : TILE_N, (int)a.N - n0);
+    const uint16_t* out = static_cast<const uint16_t*>(a.out);
+    const uint16_t* g = static_cast<const uint16_t*>(a.next_norm_w);
+    uint16_t* xn = static_cast<uint16_t*>(a.xn_out);
+    const int64_t part = (int64_t)tile * splits + split;
+    for (int t = warp; t < a.M; t += WORKERS / 32) {
+      float ss = 0.f;
+      for (int r = lane; r < own; r += 32) {
+        const float x0 = bf16_bits_to_float(out[t * a.ldo + n0 + r]);
+        ss = fmaf(x0, x0, ss);
+        xn[t * a.ld_xn + n0 + r] = (uint16_t)float_to_bf16_bits(x0 * bf16_bits_to_float(g[n0 + r]));
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) a.sumsq_out[part * a.M + t] = ss;
+    }
   }
 }
 
@@ -907,6 +937,12 @@ static size_t partials_bytes(int64_t M) {
   return (size_t)MAX_GRID * nt * TILE_N * sizeof(float);
 }
 
+int linear_tcgen05_parts(int fmt, int64_t M, int64_t K, int64_t N, int epilogue) {
+  if (M < 2 || M > 128 || encode_tiled() == nullptr) return 0;
+  const Plan pl = make_plan(fmt, M, K, N, epilogue);
+  return pl.tiles * pl.splits;
+}
+
 bool linear_persistent_wins(const LinearArgs& a) {
   (void)a;
   return false;  // (measured: not yet - the per-tile kernel is ahead on every shape of the benchmark)
@@ -956,6 +992,7 @@ static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) 
       return FB_ERR_MEMORY;
     }
   }
+  p.sumsq_in = a.sumsq_in, p.sumsq_parts = a.sumsq_parts;
   if (a.norm_w) {
     float* rstd = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + WS_RSTD_AT);
     uint16_t* xn = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(a.workspace) + WS_BODY_AT + shared_tiles);

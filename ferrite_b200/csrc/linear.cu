@@ -43,6 +43,33 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
   return fb::linear_gemv(a, s);
 }
 
+extern "C" int fb_linear_chain_parts(int fmt, int64_t M, int64_t K, int64_t N, int epilogue) {
+  if ((fmt != FB_BFP8 && fmt != FB_BFP4) || K % 8 || N % 16) return 0;
+  return fb::linear_tcgen05_parts(fmt, M, K, N, epilogue);
+}
+
+extern "C" int fb_linear_chained(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out, int out_dtype,
+                                 int64_t ldo, float eps, int epilogue, const void* residual, int64_t ldr, const float* sumsq_in, int sumsq_parts,
+                                 const void* next_norm_w, void* xn_out, int64_t ld_xn, float* sumsq_out, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  FB_REQUIRE(fmt == FB_BFP8 || fmt == FB_BFP4, "fb_linear_chained: W is bfp8 or bfp4 (dtype %d given)", fmt);
+  FB_REQUIRE(x && W && out, "fb_linear_chained: null pointer");
+  FB_REQUIRE(M >= 2 && M <= 128 && K >= 8 && K % 8 == 0 && N >= 16 && N % 16 == 0, "fb_linear_chained: 2 to 128 rows, K a multiple of 8, N of 16");
+  FB_REQUIRE(out_dtype == FB_BF16 || out_dtype == FB_FP32, "fb_linear_chained: out is bf16 or fp32");
+  FB_REQUIRE(epilogue >= FB_EPI_NONE && epilogue <= FB_EPI_RESIDUAL && (epilogue != FB_EPI_SWIGLU || N % 128 == 0), "fb_linear_chained: epilogue %d (SwiGLU: N a multiple of 128)", epilogue);
+  FB_REQUIRE(epilogue != FB_EPI_RESIDUAL || residual, "fb_linear_chained: the residual epilogue needs a residual");
+  FB_REQUIRE(sumsq_in || next_norm_w, "fb_linear_chained: neither takes a norm over nor hands one on (fb_linear does the rest)");
+  FB_REQUIRE(!sumsq_in || sumsq_parts >= 1, "fb_linear_chained: the sums of squares come in at least one part");
+  FB_REQUIRE(!next_norm_w || (xn_out && sumsq_out && ld_xn >= N && out_dtype == FB_BF16 && epilogue != FB_EPI_SWIGLU),
+             "fb_linear_chained: handing a norm on takes xn_out and sumsq_out, a bf16 result and no SwiGLU");
+  FB_REQUIRE(ldx >= K && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0, "fb_linear_chained: misaligned x or W");
+  fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, nullptr, eps, epilogue, residual, ldr, workspace, workspace_bytes};
+  a.sumsq_in = sumsq_in, a.sumsq_parts = sumsq_parts;
+  a.next_norm_w = next_norm_w, a.xn_out = xn_out, a.ld_xn = ld_xn, a.sumsq_out = sumsq_out;
+  FB_REQUIRE(fb::linear_tcgen05_supports(a), "fb_linear_chained: a shape the tensor-core kernel does not take");
+  return fb::linear_tcgen05(a, (cudaStream_t)stream);
+}
+
 extern "C" int fb_linear_indexed(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, int64_t x_slot_rows, const void* W, int64_t N,
                                  int n_experts, const int32_t* index, int n_slots, int sum_slots, void* out, int out_dtype, int64_t ldo,
                                  int64_t out_slot_stride, const void* norm_w, float eps, int epilogue, const void* residual, int64_t ldr,

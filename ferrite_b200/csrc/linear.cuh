@@ -21,6 +21,16 @@ struct LinearArgs {
   void* workspace;
   size_t workspace_bytes;
   bool persistent = false;  // the tcgen05 path's persistent kernel (tiles' steps shared out over the SMs) instead of a CTA per tile
+  // An RMSNorm handed from the matmul that makes its input to the matmul that consumes it (fb_linear_chained), so that no
+  // kernel stands between them.  As producer (with the residual epilogue, out bf16): besides out[t, n], xn_out[t, n] =
+  // bf16(out[t, n] * next_norm_w[n]) and sumsq_out[part * M + t] = the sum of out[t, n]^2 over the part's columns, a part
+  // per CTA.  As consumer: x is such an xn, and the row scale is rsqrt(sum over sumsq_in's parts / K + eps).
+  const void* next_norm_w = nullptr;
+  void* xn_out = nullptr;
+  int64_t ld_xn = 0;
+  float* sumsq_out = nullptr;
+  const float* sumsq_in = nullptr;
+  int sumsq_parts = 0;
 };
 
 // Tensor.matmul(index=) (ferrite/tensor.py:450-460): W a batch of packed matrices, index[slot] picks one per slot
@@ -46,7 +56,8 @@ int linear_mma(const LinearArgs& a, cudaStream_t s);      // gemm_mma.cu: up to 
 bool linear_mma_supports(const LinearArgs& a);
 int linear_tcgen05_indexed(const LinearArgs& a, const IndexedArgs& ix, cudaStream_t s);
 bool linear_tcgen05_supports(const LinearArgs& a);
-bool linear_persistent_wins(const LinearArgs& a);  // whether fb_linear, left to choose, runs the persistent kernel for this shape
+bool linear_persistent_wins(const LinearArgs& a);
+int linear_tcgen05_parts(int fmt, int64_t M, int64_t K, int64_t N, int epilogue);  // CTAs (parts of sumsq_out) of the per-tile kernel's launch; 0: no chaining  // whether fb_linear, left to choose, runs the persistent kernel for this shape
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N);
 
 }  // namespace fb

@@ -112,6 +112,36 @@ def linear(x, w, out=None, out_dtype="bf16", norm_w=None, eps=1e-5, epilogue="no
     return out
 
 
+def chain_parts(w, M, epilogue="none"):
+    """How many parts the sums of squares of fb_linear_chained's result come in for this shape; 0: it cannot hand a norm on."""
+    epi = {"none": _lib.EPI_NONE, "swiglu": _lib.EPI_SWIGLU, "residual": _lib.EPI_RESIDUAL}[epilogue]
+    return lib().fb_linear_chain_parts(w.code, M, w.K, w.N, epi)
+
+
+def linear_chained(x, w, out=None, out_dtype="bf16", eps=1e-5, epilogue="none", residual=None, norm_in=None, next_norm_w=None):
+    """fb_linear_chained: x @ w with an RMSNorm taken over from the matmul before (norm_in = (sumsq, parts): x is that
+    matmul's xn) and / or handed on to the one after (next_norm_w: returns (out, xn, sumsq, parts) instead of out)."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and w.batch == 1 and x.shape[1] == w.K
+    M = x.shape[0]
+    epi = {"none": _lib.EPI_NONE, "swiglu": _lib.EPI_SWIGLU, "residual": _lib.EPI_RESIDUAL}[epilogue]
+    cols = w.N // 2 if epilogue == "swiglu" else w.N
+    if out is None:
+        out = torch.empty(M, cols, dtype=_TORCH[out_dtype], device=x.device)
+    xn = sumsq = None
+    parts = 0
+    if next_norm_w is not None:
+        parts = chain_parts(w, M, epilogue)
+        assert parts, "this shape cannot hand a norm on"
+        xn = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+        sumsq = torch.empty(parts, M, dtype=torch.float32, device=x.device)
+    check(lib().fb_linear_chained(w.code, x.data_ptr(), M, w.K, x.stride(0), w.data.data_ptr(), w.N, out.data_ptr(), _lib.DTYPES[out_dtype], out.stride(0),
+                                  eps, epi, _ptr(residual), residual.stride(0) if residual is not None else 0,
+                                  _ptr(norm_in[0]) if norm_in else None, norm_in[1] if norm_in else 0, _ptr(next_norm_w), _ptr(xn),
+                                  xn.stride(0) if xn is not None else 0, _ptr(sumsq), None, 0, _stream()))
+    count()
+    return (out, xn, sumsq, parts) if next_norm_w is not None else out
+
+
 def gather_rows(table, ids, out=None):
     """table[ids] for a 2-D table and an int32 vector of ids on the device (Tensor.gather)."""
     assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32 and ids.dim() == 1

@@ -690,8 +690,9 @@ def _packed_matmul(t):
     return None
 
 
-def _fused_linear(t, into):
-    """t as one fb_linear call with an epilogue, where its tree is a block's SwiGLU or residual add; else False."""
+def _fused_linear(t, into, hand_on=None):
+    """t as one fb_linear call with an epilogue, where its tree is a block's SwiGLU or residual add; else False.
+    hand_on: the weight of the RMSNorm the result goes through next (see _linear): only a residual add takes it."""
     if t.op == "mul" and t.dtype == "bf16":  # silu(mm[:, :m]) * mm[:, m:]
         for g, u in (t.srcs, t.srcs[::-1]):
             gate = _match_silu_of(g)
@@ -712,26 +713,50 @@ def _fused_linear(t, into):
     if t.op == "add" and t.dtype == "bf16":  # x + mm
         for x, mm in (t.srcs, t.srcs[::-1]):
             if isinstance(x, Tensor) and _packed_matmul(mm) and x.shape == mm.shape == t.shape and x.dtype == "bf16" and mm.dtype == "bf16":
-                _linear(t, mm, "residual", x, into)
+                _linear(t, mm, "residual", x, into, hand_on)
                 return True
     return False
 
 
-def _linear(t, mm, epilogue, residual, into):
-    """fb_linear for the matmul mm (with its RMSNorm prologue, if its A is one) and the epilogue, into t."""
+def _linear(t, mm, epilogue, residual, into, hand_on=None):
+    """fb_linear for the matmul mm (with its RMSNorm prologue, if its A is one) and the epilogue, into t.
+
+    An RMSNorm between two block-float matmuls costs no kernel of its own where the first can hand it to the second
+    (fb_linear_chained): when mm's A is rms(x) and x is a residual add of a block-float matmul not yet computed, that
+    matmul is run with this norm's weight (hand_on) and leaves, beside x, x * g in bf16 and the rows' sums of squares;
+    mm then reads those.  x is computed either way, for whoever else reads it (the next residual add)."""
     a, w = mm.srcs
     rms = _match_rms(a)
     x, norm_w, eps = rms if rms else (a, None, 0.0)
+    w = w.realize()
+    taken = None  # (x * g, sums of squares, parts) left by the matmul that made x
+    # (9 rows and more: fewer go to the register-fed kernel, which takes no norm over)
+    if rms and x.op == "add" and x.dtype == "bf16" and x.batch == 1 and 9 <= x.rows <= 128:
+        norm_w = norm_w.realize()
+        if norm_w.buf.is_contiguous() and _fused_linear(x, None, hand_on=norm_w):
+            taken = x.args.pop("handed", {}).get(id(norm_w))
     x = x.realize()
-    xb = x.buf[0] if x.buf.stride(2) == 1 and x.buf.stride(1) % 8 == 0 else (x + 0).realize().buf[0]
     res = None
     if residual is not None:
         residual = residual.realize()
         res = residual.buf[0] if residual.buf.stride(2) == 1 else (residual + 0).realize().buf[0]
-    w = w.realize()
     out = into if into is not None and into.buf.stride(2) == 1 else Tensor(t.rt, t.rows, t.cols, dtype=t.dtype)
-    ops.linear(xb, w.packed, out=out.buf[0], out_dtype=t.dtype, norm_w=None if norm_w is None else norm_w.buf, eps=eps, epilogue=epilogue, residual=res)
-    t.rt.launched("linear " + w.dtype + (" rms" if rms else "") + ("" if epilogue == "none" else " " + epilogue))
+    name = "linear " + w.dtype + (" rms" if rms else "") + ("" if epilogue == "none" else " " + epilogue)
+    give = hand_on is not None and epilogue == "residual" and t.dtype == "bf16" and 9 <= t.rows <= 128 and ops.chain_parts(w.packed, t.rows, epilogue)
+    if taken or give:
+        xb = taken[0] if taken else (x.buf[0] if x.buf.stride(2) == 1 and x.buf.stride(1) % 8 == 0 else (x + 0).realize().buf[0])
+        if rms and not taken:  # (a norm that nobody handed over: computed on its own, then the chained call reads plain rows)
+            xb = ops.rmsnorm(xb, norm_w.buf.reshape(-1), eps)
+        got = ops.linear_chained(xb, w.packed, out=out.buf[0], out_dtype=t.dtype, eps=eps, epilogue=epilogue, residual=res,
+                                 norm_in=taken[1:] if taken else None, next_norm_w=hand_on.buf if give else None)
+        if give:
+            t.args = dict(t.args, handed={id(hand_on): (got[1], got[2], got[3])})
+        t.rt.launched(name + " chained")
+        _done(t, buf=out.buf)
+        return
+    xb = x.buf[0] if x.buf.stride(2) == 1 and x.buf.stride(1) % 8 == 0 else (x + 0).realize().buf[0]
+    ops.linear(xb, w.packed, out=out.buf[0], out_dtype=t.dtype, norm_w=None if norm_w is None else norm_w.realize().buf, eps=eps, epilogue=epilogue, residual=res)
+    t.rt.launched(name)
     _done(t, buf=out.buf)
 
 

@@ -117,6 +117,21 @@ int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const v
 enum fb_linear_kernel { FB_LINEAR_AUTO = 0, FB_LINEAR_TCGEN05 = 1, FB_LINEAR_GEMV = 2, FB_LINEAR_MMA = 3, FB_LINEAR_PERSISTENT = 4 };
 int fb_linear_prefer(int kernel);
 
+/* fb_linear with an RMSNorm handed from the matmul that makes its input to the matmul that consumes it, so that no
+ * kernel stands between the two (a decoder block's x + o_proj(...) -> rms -> gate_up, and down_proj -> next block's rms ->
+ * qkv: models/llama.py:95-109, 82-85).  No counterpart in the reference, whose fused kernels are generated per tree.
+ *   As producer (next_norm_w given; FB_EPI_RESIDUAL or none, out bf16): besides out, xn_out[t, n] = bf16(out[t, n] *
+ *   next_norm_w[n]) (rows ld_xn apart) and sumsq_out[part * M + t] = sum over the part's columns of out[t, n]^2, one part
+ *   per CTA of the launch: fb_linear_chain_parts(fmt, M, K, N, epilogue) parts (0: this shape cannot chain).
+ *   As consumer (sumsq_in given): x is such an xn_out, and the accumulators are scaled by rsqrt(sum of the sumsq_in parts
+ *   / K + eps) - what the RMSNorm prologue of fb_linear computes, without its pass over x.
+ * A call may be both.  2 <= M <= 128; runs the tcgen05 kernel (a CTA per tile) whatever fb_linear_prefer says. */
+int fb_linear_chain_parts(int fmt, int64_t M, int64_t K, int64_t N, int epilogue);
+int fb_linear_chained(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out, int out_dtype,
+                      int64_t ldo, float eps, int epilogue, const void* residual, int64_t ldr, const float* sumsq_in, int sumsq_parts,
+                      const void* next_norm_w, void* xn_out, int64_t ld_xn, float* sumsq_out, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
 /* Tensor.matmul(index=) (ferrite/tensor.py:450-460; ferrite/compiler.py:704-706): a mixture of experts' matmul.  W is
  * a batch of n_experts packed [K, N] matrices fb_packed_bytes(fmt, K, N) apart; index[slot] (int32, read on the
  * device, so a replayed step follows its tokens' choices) picks one for each of n_slots slots, and a slot that picks

@@ -162,3 +162,30 @@ def test_persistent_kernel(cuda, prefer, fmt, M, K, N, norm, epilogue):
     assert rel_err(to_numpy(got), want) < (4e-3 if norm else 2e-5)
     from ferrite_b200._lib import lib
     assert lib().fb_status_word() == 0, "no wait gave up"
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("M,K,N,N2", [(32, 4096, 4096, 2048), (9, 1024, 512, 256), (128, 512, 1088, 128), (33, 14336, 4096, 512)])
+def test_norm_handed_from_one_matmul_to_the_next(cuda, fmt, M, K, N, N2):
+    # x1 = r + x @ W1; y = silu-less next matmul of rms(x1) * g: the first matmul leaves bf16(x1 * g) and the rows' sums of
+    # squares in parts (one per CTA), the second scales its accumulators by them - against the oracle, and against the
+    # same two matmuls with the norm as fb_linear's own prologue (the same x1 bit for bit; y within a rounding of fp32 sums)
+    rng = np.random.default_rng(M + K + N)
+    x, w1, tx, p1 = case(rng, M, K, N, fmt, cuda)
+    w2 = bfp.bf16_round(rng.normal(0, 0.02, (N, N2)).astype(np.float32))
+    p2 = ops.quantize(to_bf16_tensor(w2, cuda), fmt)
+    r = bfp.bf16_round(rng.normal(0, 1, (M, N)).astype(np.float32))
+    g = bfp.bf16_round(rng.normal(1, 0.1, (1, N)).astype(np.float32))
+    tr, tg = to_bf16_tensor(r, cuda), to_bf16_tensor(g, cuda)
+    x1_plain = ops.linear(tx, p1, epilogue="residual", residual=tr)
+    y_plain = ops.linear(x1_plain, p2, norm_w=tg, eps=1e-5, out_dtype="fp32")
+    x1, xn, sumsq, parts = ops.linear_chained(tx, p1, epilogue="residual", residual=tr, next_norm_w=tg)
+    assert parts == ops.chain_parts(p1, M, "residual") and sumsq.shape == (parts, M)
+    assert torch.equal(x1, x1_plain), "the handed-on norm does not change the matmul's own result"
+    x1f = x1.float()
+    assert torch.equal(xn, (x1f * tg.float()).bfloat16()), "xn is bf16(x1 * g)"
+    assert torch.allclose(sumsq.sum(0), (x1f * x1f).sum(1), rtol=1e-5)
+    y = ops.linear_chained(xn, p2, out_dtype="fp32", eps=1e-5, norm_in=(sumsq, parts))
+    want = llama.rms(to_numpy(x1), g, 1e-5) @ bfp.bfp(w2, fmt)
+    assert rel_err(to_numpy(y), want) < 4e-3
+    assert rel_err(to_numpy(y), to_numpy(y_plain)) < 1e-5

@@ -26,6 +26,11 @@ from ._lib import check, lib
 BFP = ("bfp8", "bfp4")
 _TORCH = {"bf16": torch.bfloat16, "fp32": torch.float32, "int32": torch.int32}
 _NAME = {v: k for k, v in _TORCH.items()}
+# Whether the planner hands an RMSNorm from the matmul that makes its input to the matmul that consumes it
+# (fb_linear_chained) instead of running the norm's preparation as a kernel of its own.  Off: measured on the 8B-shape
+# step it saves 64 launches and still costs time (5.21 ms against 5.01): the preparation kernel hides behind the next
+# matmul's set-up, while the hand-over adds a pass at the end of the producing matmul and a sum over its 128 parts.
+CHAIN_NORMS = False
 FIDELITY = 4  # accepted and ignored, as the numpy reference ignores it (models/llama.py:33): products are exact here
 
 # elementwise opcodes of fb_elementwise (include/ferrite_b200.h)
@@ -731,7 +736,7 @@ def _linear(t, mm, epilogue, residual, into, hand_on=None):
     w = w.realize()
     taken = None  # (x * g, sums of squares, parts) left by the matmul that made x
     # (9 rows and more: fewer go to the register-fed kernel, which takes no norm over)
-    if rms and x.op == "add" and x.dtype == "bf16" and x.batch == 1 and 9 <= x.rows <= 128:
+    if CHAIN_NORMS and rms and x.op == "add" and x.dtype == "bf16" and x.batch == 1 and 9 <= x.rows <= 128:
         norm_w = norm_w.realize()
         if norm_w.buf.is_contiguous() and _fused_linear(x, None, hand_on=norm_w):
             taken = x.args.pop("handed", {}).get(id(norm_w))

@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libferrite_b200.so")
 BF16, FP32, INT32, BFP8, BFP4 = 0, 1, 2, 3, 4
 DTYPES = {"bf16": BF16, "fp32": FP32, "int32": INT32, "bfp8": BFP8, "bfp4": BFP4}
 EPI_NONE, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 2
-LINEAR_AUTO, LINEAR_TCGEN05, LINEAR_GEMV, LINEAR_MMA, LINEAR_PERSISTENT = 0, 1, 2, 3, 4  # fb_linear_prefer
+LINEAR_AUTO, LINEAR_TCGEN05, LINEAR_GEMV, LINEAR_MMA, LINEAR_PERSISTENT, LINEAR_GEMV_STREAM = 0, 1, 2, 3, 4, 5  # fb_linear_prefer
 
 _p, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 

@@ -28,6 +28,6 @@ extern "C" int fb_version(void) { return 1; }
 extern "C" const char* fb_last_error(void) { return fb::g_error; }
 
 extern "C" int fb_status_word(void) {
-  const int a = fb::status_word_tcgen05(), b = fb::status_word_peer();  // (both read, so both are cleared)
-  return a ? a : b;
+  const int a = fb::status_word_tcgen05(), b = fb::status_word_peer(), c = fb::status_word_gemv_stream();  // (all read, so all are cleared)
+  return a ? a : b ? b : c;
 }

@@ -17,6 +17,7 @@ int launch_status(const char* what);  // cudaGetLastError() -> FB_OK / FB_ERR_LA
 // the status words of the kernels that wait (each reads and clears its own): 0, or the code of the wait that gave up
 int status_word_tcgen05();
 int status_word_peer();
+int status_word_gemv_stream();
 
 #define FB_REQUIRE(cond, ...)            \
   do {                                   \

@@ -5,7 +5,8 @@
 // the kernel stays bound by the HBM stream of packed weights, which it reads exactly once:
 //
 //   x producer   (1 thread)  TMA tiles [tokens x 64] of the (normalised) activations, 128B-swizzled     -> smem ring
-//   x producer (same thread) cp.async.bulk.prefetch.L2 of the packed weights ten steps ahead
+//                            (the packed weights are NOT prefetched into L2: the workers' own loads stream at the full
+//                            HBM rate, and a bulk L2 prefetch running ten steps ahead was measured to cost 5 %)
 //   16 worker warps          in 4 teams, each taking every fourth step: packed bytes by 128-bit global loads into
 //                            registers that are refilled for the team's next step as soon as they are unpacked (no
 //                            staging in shared memory, whose bandwidth the bf16 operand tiles need) -> bf16 pairs
@@ -38,7 +39,6 @@ constexpr int WORKERS = 512;    // one CTA per SM (a kernel that allocates tenso
 constexpr int WARP_MMA = 16, WARP_X = 18;  // warps 16 and 17 issue MMAs
 constexpr int THREADS = 19 * 32;
 constexpr int TEAMS = 4;        // teams of worker warps, each unpacking every fourth step on its own
-constexpr int PREFETCH = 10;    // steps of K the L2 prefetch runs ahead
 constexpr int A_SLOT_BYTES = TILE_N * STEP_ROWS * 2;
 constexpr int MAX_STAGES = 8;
 // workspace (linear.cuh): arrival words of the persistent kernel's CTAs | row scales | partial tiles | normalised activations
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   const uint32_t abort_flag = smem_u32(tmem_slot + 1);
 
   // The kernel is launched as a programmatic dependent of the kernel before it: everything up to a griddep_wait()
-  // (barriers, tensor memory, the first weight loads and their L2 prefetch - weights are never written by a kernel of
+  // (barriers, tensor memory, the first weight loads - weights are never written by a kernel of
   // the stream) overlaps that kernel's last CTAs; the activations, row scales, residual and expert index are read after.
   griddep_launch_dependents();
   if (p.mode != 0) griddep_wait();  // the expert index decides what is read at all
@@ -180,25 +180,13 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       tok_rstd[t] = rs;
       tok_scale[t] = p.row_scale && t < a.M ? bf16_bits_to_float(p.row_scale[(int64_t)zslot * a.M + t]) : 1.f;
     }
-  } else if (warp == WARP_X && lane <= PREFETCH) {
+  } else if (warp == WARP_X && lane == 0) {
     Ring rx;
     int ks = s0 % S, slot = s0 / S;
     const int y = p.mode == 1 ? (int)(zslot * p.x_slot_rows) : 0;
-    // The packed weights are pulled into L2 PREFETCH steps ahead of the workers' loads, so those find them at L2
-    // latency: a handful of loads in flight per thread then covers the HBM stream (no staging, no registers).
-    const uint8_t* Wp = static_cast<const uint8_t*>(a.W) + (p.mode == 1 ? expert * p.expert_bytes : 0);
-    auto prefetch = [&](int step) {
-      if (p.mode == 2 || step >= n_steps) return;
-      const int64_t first = (int64_t)(s0 + step) * STEP_UNITS;
-      const int units = min((int64_t)STEP_UNITS, KS - first);
-      if (units <= 0) return;
-      bulk_prefetch_l2(Wp + (g0 * KS + first) * UNIT, units * UNIT);
-      if (has_g1) bulk_prefetch_l2(Wp + (g1 * KS + first) * UNIT, units * UNIT);
-    };
-    if (lane == 0) prefetch_tensormap(&tmap_x);
-    else prefetch(lane - 1);  // the first steps' bytes, asked for by a lane each
-    if (lane == 0) griddep_wait();  // the activations come from the kernel before
-    for (int i = 0; lane == 0 && i < n_steps; ++i, rx.next(SX)) {
+    prefetch_tensormap(&tmap_x);
+    griddep_wait();  // the activations come from the kernel before
+    for (int i = 0; i < n_steps; ++i, rx.next(SX)) {
       const int s = rx.slot;
       mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
       mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
@@ -207,7 +195,6 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       for (int u = 0; u < STEP_UNITS; ++u)  // rows of K past the end read as zeros (or meet zeros in A)
         tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, x0 + u * KSTEP, y, smem_u32(x_full + s));
       if (++ks == S) ks = 0, ++slot;
-      prefetch(i + PREFETCH);
     }
   } else if ((warp == WARP_MMA || warp == WARP_MMA + 1) && lane == 0) {
     const int me = warp - WARP_MMA;  // steps me, me + 2, ... into accumulator `me`
@@ -489,8 +476,8 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
 // Arrival words are cleared by the owner; the next launch touches them only after its griddep_wait(), i.e. after this
 // grid has finished.
 //
-// Warps: 0-15 unpack (4 teams), 16 and 17 issue MMAs, 18 feeds activations and the L2 prefetch, 19 idles, 20-23 run the
-// epilogues.  The unpacking warps need ~96 registers, the others few: the kernel is compiled for 768 threads (80 each)
+// Warps: 0-15 unpack (4 teams; together they also run the epilogue of the run's last segment), 16 and 17 issue MMAs, 18 feeds
+// activations, 19 idles, 20-23 run the epilogues.  The unpacking warps need ~96 registers, the others few: the kernel is compiled for 768 threads (80 each)
 // and setmaxnreg moves registers from warps 16-19 to the unpacking warps.
 constexpr int P_THREADS = 24 * 32, WARP_EPI = 20;
 
@@ -562,6 +549,105 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
   // the two 64-column groups of a tile: neighbours, or a group of gate columns and the group of their up columns
   auto groups = [&](int tile, int& g0, int& g1) { g0 = swiglu ? tile : 2 * tile, g1 = swiglu ? tile + G / 2 : 2 * tile + 1; };
   const uint8_t* W = static_cast<const uint8_t*>(a.W);
+
+  // ---- a segment's epilogue for quarter qd of the TMEM lanes (tile rows 32 qd .. 32 qd + 31, a row per lane): passes
+  // of 16 tokens first_pass, first_pass + pass_stride, ...  The row scales come from shared memory (the epilogue warps'
+  // copy) or, with rs == nullptr, from where the norm's kernel left them.
+  struct SegmentEnd {
+    bool tail;   // the segment does not start its tile: its sums went to the tile's owner
+    int others;  // CTAs after this one whose sums of an owned tile were added
+  };
+  auto epilogue = [&](auto pass_width, int s, int qd, int first_pass, int pass_stride, const float* rs) -> SegmentEnd {
+    constexpr int PW = decltype(pass_width)::value;  // tokens a pass: 16, or 8 where more warps share a segment
+    const int row = 32 * qd + lane;
+    const Segment g = segment(s);
+    const int pair = s & 1;
+    const bool whole_end = g.k_first + g.k_steps == S;  // the segment reaches the tile's last step
+    const bool tail = g.k_first > 0;
+    const int64_t n = swiglu ? 64 * (int64_t)g.tile + 16 * qd + (lane & 15) : TILE_N * (int64_t)g.tile + row;
+    const bool live = swiglu ? lane < 16 && n < a.N / 2 : n < a.N;
+    // the CTAs after this one that hold the rest of an owned tile: c + 1 .. while their runs begin inside the tile
+    int others = 0;
+    if (!tail && !whole_end) {
+      const int64_t tile_end = (int64_t)(g.tile + 1) * S;
+      while ((int)blockIdx.x + others + 1 < (int)gridDim.x && (int64_t)(blockIdx.x + others + 1) * p.work / gridDim.x < tile_end) ++others;
+    }
+    mbar_wait(smem_u32(acc_full + pair), (uint32_t)(s >> 1) & 1, abort_flag, WAIT_ACC);
+    tc_fence_after();
+    for (int o = lane; o < others; o += 32) {  // a lane per CTA waited for (every warp waits for itself)
+      const uint32_t* flag = p.arrived + blockIdx.x + 1 + o;
+      const long long start = clock64();
+      for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v || ld_shared_volatile(abort_flag)) break;
+        if (clock64() - start > WAIT_CLOCKS) {
+          asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
+          atomicCAS(&g_status_word, 0, (int)WAIT_SHARED_TILE);
+          break;
+        }
+        __nanosleep(32);
+      }
+    }
+    __syncwarp();
+    const bool even = g.k_steps > 1 || !(g.i_first & 1), odd = g.k_steps > 1 || (g.i_first & 1);  // which accumulators hold steps
+    const uint32_t acc = tmem + ((uint32_t)(32 * qd) << 16) + 2 * pair * nt;
+    float* mine = p.partials + (size_t)blockIdx.x * nt * TILE_N;
+    // PW tokens at a time (nt is a multiple of 16), one kind of load after another, every load of a kind in flight
+    // before the first is used: a pass is ONE trip to tensor memory, one per CTA whose sums are added, one to the
+    // residual - not one per token, and the arithmetic is PW independent chains
+    for (int c0 = PW * first_pass; c0 < nt && c0 < a.M; c0 += PW * pass_stride) {
+      float v[PW], w[PW];
+      if constexpr (PW == 16) {
+        if (even) tmem_ld16_nowait(acc + c0, v);
+        if (odd) tmem_ld16_nowait(acc + nt + c0, w);
+      } else {
+        if (even) tmem_ld8_nowait(acc + c0, v);
+        if (odd) tmem_ld8_nowait(acc + nt + c0, w);
+      }
+      tmem_ld_wait();
+      if (odd) {
+#pragma unroll
+        for (int e = 0; e < PW; ++e) v[e] = even ? v[e] + w[e] : w[e];
+      }
+      if (tail) {
+#pragma unroll
+        for (int e = 0; e < PW; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
+        continue;
+      }
+      for (int o = 0; o < others; ++o) {  // the rest of the tile, added in CTA order
+        const float* theirs = p.partials + (size_t)(blockIdx.x + 1 + o) * nt * TILE_N + (size_t)c0 * TILE_N + row;
+#pragma unroll
+        for (int e = 0; e < PW; ++e) w[e] = c0 + e < a.M ? __ldcg(theirs + e * TILE_N) : 0.f;
+#pragma unroll
+        for (int e = 0; e < PW; ++e) v[e] += w[e];
+      }
+#pragma unroll
+      for (int e = 0; e < PW; ++e) v[e] *= rs ? rs[c0 + e] : p.rstd && c0 + e < a.M ? p.rstd[c0 + e] : 1.f;
+      if (swiglu) {
+#pragma unroll
+        for (int e = 0; e < PW; ++e) w[e] = __shfl_down_sync(0xffffffffu, v[e], 16);
+#pragma unroll
+        for (int e = 0; e < PW; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * w[e];
+      } else if (a.epilogue == FB_EPI_RESIDUAL) {
+#pragma unroll
+        for (int e = 0; e < PW; ++e)
+          w[e] = live && c0 + e < a.M ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[(c0 + e) * a.ldr + n]) : 0.f;
+#pragma unroll
+        for (int e = 0; e < PW; ++e) v[e] += w[e];
+      }
+#pragma unroll
+      for (int e = 0; e < PW; ++e) {
+        const int t = c0 + e;
+        if (t < a.M && live) {
+          const int64_t at = t * a.ldo + n;
+          if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = v[e];
+          else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(v[e]);
+        }
+      }
+    }
+    return SegmentEnd{tail, others};
+  };
 
   if (warp < WORKERS / 32) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
@@ -638,31 +724,23 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
       if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
       for (int t = 0; t < TEAMS; ++t) ra.next(SA);
     }
+    // The run's last segment has no main loop to hide its epilogue behind, and a warp's stores to global memory are
+    // slow (tens of cycles each, one per token): the sixteen unpacking warps, idle by now, share it - four to a quarter
+    // of the TMEM lanes, each taking every fourth pass of 8 tokens.
+    if (n_segments > 0) {
+      griddep_wait();
+      const SegmentEnd e = epilogue(std::integral_constant<int, 8>{}, n_segments - 1, warp & 3, warp >> 2, 4, nullptr);
+      if (e.tail) __threadfence();
+      asm volatile("bar.sync 3, 640;" ::: "memory");
+    }
   } else if (warp < WARP_EPI) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
-    if (warp == WARP_X && lane <= PREFETCH) {
+    if (warp == WARP_X && lane == 0) {
       Ring rx;
-      // packed weights PREFETCH steps ahead into L2 (see the kernel above)
-      auto prefetch = [&](int step, At at) {
-        if (step >= n_steps) return;
-        const int first = at.ks * STEP_UNITS, units = min(STEP_UNITS, KS - first);
-        if (units <= 0) return;
-        int g0, g1;
-        groups(at.tile, g0, g1);
-        bulk_prefetch_l2(W + (int64_t)(g0 * KS + first) * UNIT, units * UNIT);
-        if (g1 < G) bulk_prefetch_l2(W + (int64_t)(g1 * KS + first) * UNIT, units * UNIT);
-      };
-      At ahead{tile_lo, k_lo};  // the step the prefetch has reached
-      if (lane == 0) {
-        prefetch_tensormap(&tmap_x);
-        ahead.advance(PREFETCH, S);
-      } else {
-        ahead.advance(lane - 1, S);
-        prefetch(lane - 1, ahead);  // the first steps' bytes, asked for by a lane each
-      }
-      if (lane == 0) griddep_wait();  // the activations come from the kernel before
+      prefetch_tensormap(&tmap_x);
+      griddep_wait();  // the activations come from the kernel before
       int ks = k_lo;
-      for (int i = 0; lane == 0 && i < n_steps; ++i, rx.next(SX)) {
+      for (int i = 0; i < n_steps; ++i, rx.next(SX)) {
         const int s = rx.slot;
         mbar_wait(smem_u32(x_empty + s), rx.phase ^ 1, abort_flag, WAIT_X_EMPTY);
         mbar_expect_tx(smem_u32(x_full + s), x_slot_bytes);
@@ -670,8 +748,6 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
         for (int u = 0; u < STEP_UNITS; ++u)
           tma_load_2d(smem_u32(sX + s * x_slot_bytes + u * nt * 128), &tmap_x, ks * STEP_ROWS + u * KSTEP, 0, smem_u32(x_full + s));
         if (++ks == S) ks = 0;
-        prefetch(i + PREFETCH, ahead);
-        ahead.advance(1, S);
       }
     } else if ((warp == WARP_MMA || warp == WARP_MMA + 1) && lane == 0) {
       const int me = warp - WARP_MMA;  // steps me, me + 2, ... of the run; segment s into accumulator me of pair s % 2
@@ -706,102 +782,27 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
       }
     }
   } else {
-    // ---- the epilogue warps: warp 20 + q reads quarter q of the TMEM lanes (tile rows 32q .. 32q + 31), all tokens
+    // ---- the epilogue warps: warp 20 + q reads quarter q of the TMEM lanes (tile rows 32q .. 32q + 31)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
-    const int qd = warp - WARP_EPI, row = 32 * qd + lane, etid = tid - WARP_EPI * 32;
+    const int qd = warp - WARP_EPI, etid = tid - WARP_EPI * 32;
     griddep_wait();  // the row scales, the residual and the arrival words are the work of kernels before this one
     for (int t = etid; t < 128; t += 128) tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
     asm volatile("bar.sync 2, 128;" ::: "memory");
     for (int s = 0; s < n_segments; ++s) {
-      const Segment g = segment(s);
-      const int pair = s & 1;
-      const bool whole_end = g.k_first + g.k_steps == S;  // the segment reaches the tile's last step
-      const bool tail = g.k_first > 0;                    // it does not start the tile: its sums go to the tile's owner
-      const int64_t n = swiglu ? 64 * (int64_t)g.tile + 16 * qd + (lane & 15) : TILE_N * (int64_t)g.tile + row;
-      const bool live = swiglu ? lane < 16 && n < a.N / 2 : n < a.N;
-      // the CTAs after this one that hold the rest of an owned tile: c + 1 .. while their runs begin inside the tile
-      int others = 0;
-      if (!tail && !whole_end) {
-        const int64_t tile_end = (int64_t)(g.tile + 1) * S;
-        while ((int)blockIdx.x + others + 1 < (int)gridDim.x && (int64_t)(blockIdx.x + others + 1) * p.work / gridDim.x < tile_end) ++others;
-      }
-      mbar_wait(smem_u32(acc_full + pair), (uint32_t)(s >> 1) & 1, abort_flag, WAIT_ACC);
-      tc_fence_after();
-      for (int o = lane; o < others; o += 32) {  // a lane per CTA waited for (every epilogue warp waits for itself)
-        const uint32_t* flag = p.arrived + blockIdx.x + 1 + o;
-        const long long start = clock64();
-        for (;;) {
-          uint32_t v;
-          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-          if (v || ld_shared_volatile(abort_flag)) break;
-          if (clock64() - start > WAIT_CLOCKS) {
-            asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
-            atomicCAS(&g_status_word, 0, (int)WAIT_SHARED_TILE);
-            break;
-          }
-          __nanosleep(32);
-        }
-      }
-      __syncwarp();
-      const bool even = g.k_steps > 1 || !(g.i_first & 1), odd = g.k_steps > 1 || (g.i_first & 1);  // which accumulators hold steps
-      const uint32_t acc = tmem + ((uint32_t)(32 * qd) << 16) + 2 * pair * nt;
-      float* mine = p.partials + (size_t)blockIdx.x * nt * TILE_N;
-      // 16 tokens at a time (nt is a multiple of 16), one kind of load after another, every load of a kind in flight
-      // before the first is used: a pass is ONE trip to tensor memory, one per CTA whose sums are added, one to the
-      // residual - not one per token, and the arithmetic is sixteen independent chains
-      for (int c0 = 0; c0 < nt && c0 < a.M; c0 += 16) {
-        float v[16], w[16];
-        if (even) tmem_ld16_nowait(acc + c0, v);
-        if (odd) tmem_ld16_nowait(acc + nt + c0, w);
-        tmem_ld_wait();
-        if (odd) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = even ? v[e] + w[e] : w[e];
-        }
-        if (tail) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) mine[(c0 + e) * TILE_N + row] = v[e];
-          continue;
-        }
-        for (int o = 0; o < others; ++o) {  // the rest of the tile, added in CTA order
-          const float* theirs = p.partials + (size_t)(blockIdx.x + 1 + o) * nt * TILE_N + (size_t)c0 * TILE_N + row;
-#pragma unroll
-          for (int e = 0; e < 16; ++e) w[e] = c0 + e < a.M ? __ldcg(theirs + e * TILE_N) : 0.f;
-#pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] += w[e];
-        }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] *= tok_rstd[c0 + e];
-        if (swiglu) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) w[e] = __shfl_down_sync(0xffffffffu, v[e], 16);
-#pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * w[e];
-        } else if (a.epilogue == FB_EPI_RESIDUAL) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            w[e] = live && c0 + e < a.M ? bf16_bits_to_float(static_cast<const uint16_t*>(a.residual)[(c0 + e) * a.ldr + n]) : 0.f;
-#pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] += w[e];
-        }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int t = c0 + e;
-          if (t < a.M && live) {
-            const int64_t at = t * a.ldo + n;
-            if (a.out_dtype == FB_FP32) static_cast<float*>(a.out)[at] = v[e];
-            else static_cast<uint16_t*>(a.out)[at] = (uint16_t)float_to_bf16_bits(v[e]);
-          }
-        }
-      }
+      const bool last = s == n_segments - 1;
+      // (the run's last segment is the unpacking warps' work - they are idle by then, four of them to a quarter;
+      // these warps only wait for it and do the bookkeeping)
+      const SegmentEnd e = last ? epilogue(std::integral_constant<int, 8>{}, s, qd, 1 << 20, 1, tok_rstd)
+                                : epilogue(std::integral_constant<int, 16>{}, s, qd, 0, 1, tok_rstd);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(acc_empty + pair));  // this warp's quarter of the pair has been read
-      if (tail || others) {  // the four warps' partial sums are out / have been read: say so, once
-        if (tail) __threadfence();
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (etid == 0 && tail) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.arrived + blockIdx.x), "r"(1u) : "memory");
-        if (etid < others) p.arrived[blockIdx.x + 1 + etid] = 0;  // read: ready for the next launch
+      if (lane == 0) mbar_arrive(smem_u32(acc_empty + (s & 1)));  // this warp's quarter of the pair has been read
+      if (last || e.tail || e.others) {  // every warp's partial sums are out / have been read: say so, once
+        if (e.tail) __threadfence();
+        if (last) asm volatile("bar.sync 3, 640;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (etid == 0 && e.tail) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.arrived + blockIdx.x), "r"(1u) : "memory");
+        if (etid < e.others) p.arrived[blockIdx.x + 1 + etid] = 0;  // read: ready for the next launch
       }
     }
   }
@@ -943,9 +944,17 @@ int linear_tcgen05_parts(int fmt, int64_t M, int64_t K, int64_t N, int epilogue)
   return pl.tiles * pl.splits;
 }
 
+// Measured (32 tokens, bfp8, back to back in a graph): with at least a tile per SM - [4096 x 28672] with SwiGLU 36.6 us
+// against the per-tile kernel's 40.5, the [4096 x 128256] output layer 132 against 143, and the same order at 64 and 128
+// tokens - the even split of the steps beats whole tiles in waves; with fewer tiles than SMs most tiles are shared by
+// several CTAs, whose partial sums go through global memory where the per-tile kernel's clusters use shared memory, and
+// the per-tile kernel is ahead (18.8 us against 23.2 for [14336 x 4096]).
 bool linear_persistent_wins(const LinearArgs& a) {
-  (void)a;
-  return false;  // (measured: not yet - the per-tile kernel is ahead on every shape of the benchmark)
+  if (a.M < 2 || a.next_norm_w || a.sumsq_in || !linear_tcgen05_supports(a)) return false;
+  const int64_t M = a.M < 128 ? a.M : 128;
+  const size_t need = WS_BODY_AT + partials_bytes(M) + (a.norm_w ? (size_t)M * a.K * 2 : 0);
+  if (!a.workspace || a.workspace_bytes < need) return false;
+  return make_plan(a.fmt, M, a.K, a.N, a.epilogue).tiles >= sm_count();
 }
 
 size_t linear_tcgen05_workspace(int64_t M, int64_t K, int64_t N) {

@@ -5,12 +5,15 @@
 static int g_linear_kernel = FB_LINEAR_AUTO;
 
 extern "C" int fb_linear_prefer(int kernel) {
-  FB_REQUIRE(kernel >= FB_LINEAR_AUTO && kernel <= FB_LINEAR_PERSISTENT, "fb_linear_prefer: unknown kernel %d", kernel);
+  FB_REQUIRE(kernel >= FB_LINEAR_AUTO && kernel <= FB_LINEAR_GEMV_STREAM, "fb_linear_prefer: unknown kernel %d", kernel);
   g_linear_kernel = kernel;
   return FB_OK;
 }
 
-extern "C" size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N) { return fb::linear_tcgen05_workspace(M, K, N); }
+extern "C" size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+  const size_t a = fb::linear_tcgen05_workspace(M, K, N), b = M == 1 ? fb::linear_gemv_stream_workspace(K, N) : 0;
+  return a > b ? a : b;
+}
 
 extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out,
                          int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,
@@ -29,11 +32,17 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
              "fb_linear: misaligned pointer");
   fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, norm_w, eps, epilogue, residual, ldr, workspace, workspace_bytes};
   auto s = (cudaStream_t)stream;
-  // one token: the CUDA-core GEMV; a few: tensor-core MMAs whose weight fragments are unpacked in registers (no bf16
+  // one token: the CUDA-core GEMV (a CTA per 16 columns; the streaming kernel - persistent CTAs fed by bulk copies -
+  // is measured slower on every shape of the benchmark and runs only when asked for by FB_LINEAR_GEMV_STREAM); a few: tensor-core MMAs whose weight fragments are unpacked in registers (no bf16
   // tile in shared memory); more: the tcgen05 kernel, whose cost hardly grows with the tokens
   const int prefer = g_linear_kernel;
   if (prefer == FB_LINEAR_MMA && fb::linear_mma_supports(a)) return fb::linear_mma(a, s);
   if (prefer == FB_LINEAR_GEMV && M <= 4) return fb::linear_gemv(a, s);
+  if (prefer == FB_LINEAR_GEMV_STREAM) {
+    FB_REQUIRE(fb::linear_gemv_stream_supports(a), "fb_linear: [%lld, %lld] @ [%lld, %lld] is not for the streaming GEMV (one row, N a multiple of 64, the workspace given)",
+               (long long)M, (long long)K, (long long)K, (long long)N);
+    return fb::linear_gemv_stream(a, s);
+  }
   // (measured: the register-fed kernel wins for up to 8 rows on bfp4 weights and on bfp8 matrices of up to 32 M values;
   // its legacy MMAs cost about 27 cycles each per SM quarter, so beyond 8 rows the tcgen05 kernel is faster)
   const bool few_rows_win = M > 1 && M <= 8 && K <= 8192 && (fmt == FB_BFP4 || K * N <= (int64_t)32 << 20);

@@ -47,10 +47,15 @@ struct IndexedArgs {
 //   [0, 1024)     arrival words of the persistent tcgen05 kernel's CTAs: zero before the first call, and every call
 //                 leaves them zero - nothing else may ever be written here;
 //   [1024, 2048)  the row scales of an RMSNorm prologue;
-//   [2048, ...)   each kernel's own: partial tiles, the normalised activations.
-constexpr size_t WS_ARRIVED_AT = 0, WS_RSTD_AT = 1024, WS_BODY_AT = 2048;
+//   [2048, 18432) arrival counters of the streaming GEMV's output tiles (one per 64 output columns): zero before the first
+//                 call and left zero by every call, like the arrival words;
+//   [18432, ...)  each kernel's own: partial tiles and sums, the normalised activations.
+constexpr size_t WS_ARRIVED_AT = 0, WS_RSTD_AT = 1024, WS_COUNTERS_AT = 2048, WS_COUNTERS = 4096, WS_BODY_AT = WS_COUNTERS_AT + 4 * WS_COUNTERS;
 
 int linear_gemv(const LinearArgs& a, cudaStream_t s);     // gemv.cu: one token (up to 4 a pass), CUDA cores
+int linear_gemv_stream(const LinearArgs& a, cudaStream_t s);  // gemv_stream.cu: one token, persistent CTAs fed by bulk copies
+bool linear_gemv_stream_supports(const LinearArgs& a);
+size_t linear_gemv_stream_workspace(int64_t K, int64_t N);
 int linear_tcgen05(const LinearArgs& a, cudaStream_t s);  // gemm_tcgen05.cu: tensor cores (tcgen05, tiles through shared memory)
 int linear_mma(const LinearArgs& a, cudaStream_t s);      // gemm_mma.cu: up to 32 tokens, tensor cores fed from registers
 bool linear_mma_supports(const LinearArgs& a);

@@ -97,11 +97,15 @@ int fb_unpack_fields(int fmt, const void* packed, int64_t batch, int64_t K, int6
  *   acc = h @ W, fp32 accumulation, W packed [K, N] in `fmt` (FB_BFP8, FB_BFP4 or FB_BF16 row-major)
  *   epilogue (fb_epilogue), out dtype FB_BF16 or FB_FP32 (fp32: the output layer, models/llama.py:479)
  * out is [M, N] (or [M, N/2] after FB_EPI_SWIGLU), row stride ldo elements.
- * M == 1 runs as a bandwidth-bound GEMV on CUDA cores; 2..8 rows of the smaller matrices on tensor-core MMAs whose
- * weight fragments are unpacked in registers; the rest on tcgen05 tensor cores (weight tiles through shared memory,
- * accumulators in TMEM).
+ * M == 1 runs as a bandwidth-bound GEMV on CUDA cores (a CTA per 16 output columns); 2..8 rows of the smaller
+ * matrices on tensor-core MMAs whose weight fragments are unpacked in registers; the rest on tcgen05 tensor cores
+ * (weight tiles through shared memory, accumulators in TMEM): a CTA per tile of 128 columns (clusters splitting K
+ * where the tiles are few), or - with at least a tile per SM and the workspace given - one persistent CTA per SM,
+ * the tiles' steps of K shared out evenly (FB_LINEAR_PERSISTENT below).
  * workspace: fb_linear_workspace_bytes(M, K, N) bytes of device scratch (0 / NULL when that is 0):
- * it holds the normalised activations of the RMSNorm prologue between the two kernels of a call. */
+ * it holds the normalised activations of the RMSNorm prologue between the two kernels of a call, the partial sums of
+ * output tiles that several CTAs share, and their arrival counters: the first 18 KB must be ZERO before the first call
+ * that uses the buffer, and every call leaves them zero. */
 size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out,
               int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,
@@ -113,8 +117,12 @@ int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const v
  * FB_LINEAR_MMA sends every shape the register-fed kernel supports (M <= 32, K a multiple of 16) to it, one row too.
  * FB_LINEAR_PERSISTENT runs the tcgen05 path as one persistent CTA per SM, the tiles' steps of K shared out evenly and
  * tiles that several CTAs share summed through the workspace in a fixed order (one row too).
+ * FB_LINEAR_GEMV_STREAM runs one row through the streaming GEMV (persistent CTAs fed by bulk copies, each taking an equal
+ * stretch of the packed matrix; the output tiles' parts meet in the workspace and are added in a fixed order) or fails
+ * with FB_ERR_ARG where its rules do not hold: N a multiple of 64 (128 with SwiGLU), K up to ~13k (the token sits in shared
+ * memory as fp32 beside the ring), the workspace given.  Measured slower than the plain GEMV, hence never chosen.
  * The reference has one matmul kernel and no such switch (ferrite/compiler.py:699-738). */
-enum fb_linear_kernel { FB_LINEAR_AUTO = 0, FB_LINEAR_TCGEN05 = 1, FB_LINEAR_GEMV = 2, FB_LINEAR_MMA = 3, FB_LINEAR_PERSISTENT = 4 };
+enum fb_linear_kernel { FB_LINEAR_AUTO = 0, FB_LINEAR_TCGEN05 = 1, FB_LINEAR_GEMV = 2, FB_LINEAR_MMA = 3, FB_LINEAR_PERSISTENT = 4, FB_LINEAR_GEMV_STREAM = 5 };
 int fb_linear_prefer(int kernel);
 
 /* fb_linear with an RMSNorm handed from the matmul that makes its input to the matmul that consumes it, so that no

@@ -165,6 +165,51 @@ def test_persistent_kernel(cuda, prefer, fmt, M, K, N, norm, epilogue):
 
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+@pytest.mark.parametrize("K,N,norm,epilogue", [(4096, 6144, True, "none"), (4096, 4096, False, "residual"), (4096, 28672, True, "swiglu"),
+                                               (14336, 4096, False, "residual"), (100, 64, False, "none"), (64, 64, True, "none"),
+                                               (768, 2048, True, "swiglu"), (2048, 1536, False, "none"), (1024, 32064, True, "none"),
+                                               (192, 128, False, "swiglu")])
+def test_streaming_gemv(cuda, prefer, fmt, K, N, norm, epilogue):
+    # one token through the persistent kernel: stretches of units that end inside a column group, groups shared by up to
+    # eight CTAs and added in CTA order (twice the same bits), a gate group and its up group finished by whichever CTA
+    # arrives last, K that ends inside a unit (100), a matrix of one unit, one CTA for a whole small matrix - against
+    # exact products and against the CTA-per-16-columns GEMV
+    rng = np.random.default_rng(K + N)
+    x, wq, tx, packed = case(rng, 1, K, N, fmt, cuda)
+    g = bfp.bf16_round(rng.normal(1, 0.1, (1, K)).astype(np.float32)) if norm else None
+    r = bfp.bf16_round(rng.normal(0, 1, (1, N)).astype(np.float32)) if epilogue == "residual" else None
+    h = llama.rms(x.astype(np.float64), g, 1e-5) if norm else x.astype(np.float64)
+    want = h @ wq
+    if epilogue == "swiglu":
+        want = llama.glu(want[:, :N // 2], want[:, N // 2:])
+    if epilogue == "residual":
+        want = want + r
+    kw = dict(norm_w=to_bf16_tensor(g, cuda) if norm else None, eps=1e-5, epilogue=epilogue, residual=to_bf16_tensor(r, cuda) if r is not None else None)
+    prefer("GEMV_STREAM")
+    got = ops.linear(tx, packed, out_dtype="fp32", **kw)
+    again = ops.linear(tx, packed, out_dtype="fp32", **kw)
+    assert torch.equal(got, again), "shared groups are added in a fixed order, and the counters are back at zero"
+    assert rel_err(to_numpy(got), want) < 2e-5
+    got16 = ops.linear(tx, packed, **kw)
+    assert torch.equal(got16, got.bfloat16()), "bf16 output is the fp32 one rounded once"
+    prefer("GEMV")
+    plain = ops.linear(tx, packed, out_dtype="fp32", **kw)
+    assert rel_err(to_numpy(got), to_numpy(plain).astype(np.float64)) < 2e-5
+    from ferrite_b200._lib import lib
+    assert lib().fb_status_word() == 0, "no wait gave up"
+
+
+def test_streaming_gemv_refuses_what_it_does_not_take(cuda, prefer):
+    rng = np.random.default_rng(0)
+    x, wq, tx, packed = case(rng, 1, 256, 48, "bfp8", cuda)  # N is not a multiple of 64
+    want = x.astype(np.float64) @ wq
+    assert rel_err(to_numpy(ops.linear(tx, packed, out_dtype="fp32")), want) < 2e-5, "the plain GEMV takes it"
+    prefer("GEMV_STREAM")
+    with pytest.raises(Exception, match="streaming"):
+        ops.linear(tx, packed)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
 @pytest.mark.parametrize("M,K,N,N2", [(32, 4096, 4096, 2048), (9, 1024, 512, 256), (128, 512, 1088, 128), (33, 14336, 4096, 512)])
 def test_norm_handed_from_one_matmul_to_the_next(cuda, fmt, M, K, N, N2):
     # x1 = r + x @ W1; y = silu-less next matmul of rms(x1) * g: the first matmul leaves bf16(x1 * g) and the rows' sums of

@@ -337,7 +337,7 @@ def run_ferrite(args):
         "gpu_launches": int(per_step or 0) * args.steps,
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": ("the whole decode step (indexed block-float matmuls + decode attention), %d tokens" if moe else
-                                                "linear_tcgen05_kernel (block-float dequant GEMM, %d tokens)") % S, "achieved": achieved,
+                                                "linear_tcgen05_kernel / linear_persistent_kernel (block-float dequant GEMM: a CTA per tile, or persistent with at least a tile per SM; %d tokens)") % S, "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_kind,
                      "traffic": None if moe else 1.002 * lin_bytes / lin_launches,
                      "traffic_source": "not captured for the whole step" if moe else "algorithmic bytes x 1.002 (DRAM read+write of the ncu capture in profiles/, 4096x14336 bfp8, 32 tokens)",

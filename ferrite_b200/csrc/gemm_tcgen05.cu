@@ -110,9 +110,9 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
   const int x_slot_bytes = STEP_UNITS * nt * 128;  // a [tokens x 64] tile per 64 rows of K
   uint8_t* sX = sA + SA * A_SLOT_BYTES;
   uint32_t* lut = reinterpret_cast<uint32_t*>(sX + SX * x_slot_bytes);  // exponent byte -> its power of two as a bf16 pair
-  float* tok_rstd = reinterpret_cast<float*>(lut + 256);  // per token: the RMSNorm row scale, the mixture's weight (or ones)
-  float* tok_scale = tok_rstd + 128;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tok_scale + 128);
+  float* tok_rstd = reinterpret_cast<float*>(lut + 256);  // per token (nt of them): the RMSNorm row scale, the mixture's weight (or ones)
+  float* tok_scale = tok_rstd + nt;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tok_scale + nt);
   uint64_t* x_full = bars, *x_empty = bars + MAX_STAGES, *a_full = bars + 2 * MAX_STAGES, *a_empty = bars + 3 * MAX_STAGES;
   uint64_t* acc_full = bars + 4 * MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
@@ -502,8 +502,8 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
   const int x_slot_bytes = STEP_UNITS * nt * 128;
   uint8_t* sX = sA + SA * A_SLOT_BYTES;
   uint32_t* lut = reinterpret_cast<uint32_t*>(sX + SX * x_slot_bytes);
-  float* tok_rstd = reinterpret_cast<float*>(lut + 256);  // per token: the RMSNorm row scale (or 1), read by the epilogue warps only
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tok_rstd + 128);
+  float* tok_rstd = reinterpret_cast<float*>(lut + 256);  // per token (nt of them): the RMSNorm row scale (or 1), read by the epilogue warps only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tok_rstd + nt);
   uint64_t* x_full = bars, *x_empty = bars + MAX_STAGES, *a_full = bars + 2 * MAX_STAGES, *a_empty = bars + 3 * MAX_STAGES;
   uint64_t* acc_full = bars + 4 * MAX_STAGES, *acc_empty = acc_full + 2;  // one of each per accumulator pair
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
@@ -786,7 +786,7 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
     asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int qd = warp - WARP_EPI, etid = tid - WARP_EPI * 32;
     griddep_wait();  // the row scales, the residual and the arrival words are the work of kernels before this one
-    for (int t = etid; t < 128; t += 128) tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
+    for (int t = etid; t < nt; t += 128) tok_rstd[t] = p.rstd && t < a.M ? p.rstd[t] : 1.f;
     asm volatile("bar.sync 2, 128;" ::: "memory");
     for (int s = 0; s < n_segments; ++s) {
       const bool last = s == n_segments - 1;
@@ -909,7 +909,10 @@ Plan make_plan(int fmt, int64_t M, int64_t K, int64_t N, int epilogue, int slots
   // late team and take the untouched barrier of step 0 for the finished one of step 5.)
   pl.a_slots = TEAMS;  // each team refills its own slot while the tensor core reads the other teams'
   pl.x_slots = pl.nt <= 64 ? 4 : 2;
-  pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 2048 + 1024 + 5 * MAX_STAGES * 8 + 64;
+  // (alignment slack, the rings, the exponent table, two floats per token, the barriers.  Kept tight: up to 32 tokens
+  // it stays under 163 KB, the most a CTA gets from the SM's 164 KB shared-memory setting - a byte more and the SM
+  // is set to 196 KB, leaving the unpacking warps' loads 60 KB of L1 instead of 92)
+  pl.smem = 1024 + (size_t)pl.a_slots * A_SLOT_BYTES + (size_t)pl.x_slots * STEP_UNITS * pl.nt * 128 + 1024 + 2 * 4 * (size_t)pl.nt + 5 * MAX_STAGES * 8 + 64;
   return pl;
 }
 

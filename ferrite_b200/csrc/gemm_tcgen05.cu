@@ -814,39 +814,17 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
 }
 
 // x' = bf16(x * g) and rstd[t] = rsqrt(mean(x^2) + eps): the RMSNorm prologue's two factors, once per call.
-// The row scale commutes with the matmul, so the GEMM applies it to the accumulators.  A block per token; a thread
-// takes 16-byte pieces of the row (8 values), up to four of them with all their loads in flight before the first is
-// used: the kernel stands between two matmuls and is all latency (K a multiple of 8, rows 16-byte aligned).
+// The row scale commutes with the matmul, so the GEMM applies it to the accumulators.
 __global__ void __launch_bounds__(256) rms_prepare_kernel(const uint16_t* __restrict__ x, int64_t ldx, const uint16_t* __restrict__ g,
                                                           int64_t K, float eps, uint16_t* __restrict__ xn, float* __restrict__ rstd) {
   griddep_launch_dependents();
-  const int t = blockIdx.x, pieces = (int)(K / 8);
-  const uint4* xrow = reinterpret_cast<const uint4*>(x + t * ldx);
-  const uint2* grow = reinterpret_cast<const uint2*>(g);  // (the norm's weight is 8-byte aligned: two loads a piece)
-  uint4* out = reinterpret_cast<uint4*>(xn + t * K);
+  const int t = blockIdx.x;
   float ss = 0.f;
-  for (int p0 = threadIdx.x; p0 < pieces; p0 += 4 * 256) {
-    uint4 xb[4];
-    uint2 ga[4], gb[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int pc = p0 + i * 256;
-      if (pc < pieces) xb[i] = xrow[pc], ga[i] = __ldg(grow + 2 * pc), gb[i] = __ldg(grow + 2 * pc + 1);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int pc = p0 + i * 256;
-      if (pc >= pieces) break;
-      const uint32_t xw[4] = {xb[i].x, xb[i].y, xb[i].z, xb[i].w}, gw[4] = {ga[i].x, ga[i].y, gb[i].x, gb[i].y};
-      uint32_t yw[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float x0 = bf16_bits_to_float(xw[j] & 0xFFFFu), x1 = bf16_bits_to_float(xw[j] >> 16);
-        ss = fmaf(x0, x0, fmaf(x1, x1, ss));
-        yw[j] = pack_bf16x2(x0 * bf16_bits_to_float(gw[j] & 0xFFFFu), x1 * bf16_bits_to_float(gw[j] >> 16));
-      }
-      out[pc] = make_uint4(yw[0], yw[1], yw[2], yw[3]);
-    }
+  for (int64_t k = 2 * threadIdx.x; k < K; k += 2 * blockDim.x) {
+    const uint32_t xb = *reinterpret_cast<const uint32_t*>(x + t * ldx + k), gb = *reinterpret_cast<const uint32_t*>(g + k);
+    const float x0 = bf16_bits_to_float(xb & 0xFFFFu), x1 = bf16_bits_to_float(xb >> 16);
+    ss = fmaf(x0, x0, fmaf(x1, x1, ss));
+    *reinterpret_cast<uint32_t*>(xn + t * K + k) = pack_bf16x2(x0 * bf16_bits_to_float(gb & 0xFFFFu), x1 * bf16_bits_to_float(gb >> 16));
   }
   __shared__ float red[8];
   ss = warp_sum(ss);
@@ -1024,10 +1002,6 @@ static int run_pass(const LinearArgs& a, const IndexedArgs* ix, cudaStream_t s) 
     if (!a.workspace || a.workspace_bytes < need) {
       set_error("fb_linear: workspace of %zu bytes needed, %zu given (fb_linear_workspace_bytes)", need, a.workspace_bytes);
       return FB_ERR_MEMORY;
-    }
-    if ((uintptr_t)a.workspace % 16) {
-      set_error("fb_linear: the workspace is not 16-byte aligned");
-      return FB_ERR_ARG;
     }
   }
   p.sumsq_in = a.sumsq_in, p.sumsq_parts = a.sumsq_parts;

@@ -8,7 +8,7 @@ namespace fb {
 // One CTA of 8 warps per column block (per gate/up pair of blocks with the SwiGLU epilogue: warps 0-3
 // take the gate's block, 4-7 the up's).  See gemv.cuh for the per-lane work.
 template <int FMT, int M, bool NORM>
-__global__ void __launch_bounds__(256, M == 1 ? 4 : 1) linear_gemv_kernel(LinearArgs a) {
+__global__ void __launch_bounds__(256) linear_gemv_kernel(LinearArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool swiglu = a.epilogue == FB_EPI_SWIGLU;
   const int G = swiglu ? 4 : 8;

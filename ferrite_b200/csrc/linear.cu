@@ -4,6 +4,23 @@
 
 static int g_linear_kernel = FB_LINEAR_AUTO;
 
+// The head of fb_linear's workspace (arrival words, counters: linear.cuh) has to be zero before the first kernel that
+// counts in it.  A buffer this process has not been given before is zeroed here, in stream order, so that a caller's
+// fresh allocation needs no memset of its own; what the library cannot see - a buffer written by someone else between
+// calls, or freed and handed back at the same address with other contents - stays the caller's to zero.
+#include <mutex>
+static void zero_new_workspace(void* workspace, size_t bytes, cudaStream_t s) {
+  static std::mutex lock;
+  static const void* seen[64];
+  static int n_seen = 0;
+  if (!workspace || bytes < fb::WS_BODY_AT) return;
+  std::lock_guard<std::mutex> hold(lock);
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i] == workspace) return;
+  seen[n_seen < 64 ? n_seen++ : 63] = workspace;
+  cudaMemsetAsync(workspace, 0, fb::WS_BODY_AT, s);
+}
+
 extern "C" int fb_linear_prefer(int kernel) {
   FB_REQUIRE(kernel >= FB_LINEAR_AUTO && kernel <= FB_LINEAR_GEMV_STREAM, "fb_linear_prefer: unknown kernel %d", kernel);
   g_linear_kernel = kernel;
@@ -32,6 +49,7 @@ extern "C" int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t l
              "fb_linear: misaligned pointer");
   fb::LinearArgs a{fmt, x, M, K, ldx, W, N, out, out_dtype, ldo, norm_w, eps, epilogue, residual, ldr, workspace, workspace_bytes};
   auto s = (cudaStream_t)stream;
+  zero_new_workspace(workspace, workspace_bytes, s);
   // one token: the CUDA-core GEMV (a CTA per 16 columns; the streaming kernel - persistent CTAs fed by bulk copies -
   // is measured slower on every shape of the benchmark and runs only when asked for by FB_LINEAR_GEMV_STREAM); a few: tensor-core MMAs whose weight fragments are unpacked in registers (no bf16
   // tile in shared memory); more: the tcgen05 kernel, whose cost hardly grows with the tokens

@@ -104,8 +104,9 @@ int fb_unpack_fields(int fmt, const void* packed, int64_t batch, int64_t K, int6
  * the tiles' steps of K shared out evenly (FB_LINEAR_PERSISTENT below).
  * workspace: fb_linear_workspace_bytes(M, K, N) bytes of device scratch (0 / NULL when that is 0):
  * it holds the normalised activations of the RMSNorm prologue between the two kernels of a call, the partial sums of
- * output tiles that several CTAs share, and their arrival counters: the first 18 KB must be ZERO before the first call
- * that uses the buffer, and every call leaves them zero. */
+ * output tiles that several CTAs share, and their arrival counters in the first 18 KB, which every call leaves zero:
+ * fb_linear zeroes them itself (in stream order) the first time this process hands it a buffer; nobody else may write
+ * there, and a buffer that comes back after other use has to be zeroed by the caller. */
 size_t fb_linear_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int fb_linear(int fmt, const void* x, int64_t M, int64_t K, int64_t ldx, const void* W, int64_t N, void* out,
               int out_dtype, int64_t ldo, const void* norm_w, float eps, int epilogue, const void* residual,

@@ -164,6 +164,20 @@ def test_persistent_kernel(cuda, prefer, fmt, M, K, N, norm, epilogue):
     assert lib().fb_status_word() == 0, "no wait gave up"
 
 
+def test_a_workspace_the_caller_never_zeroed(cuda):
+    # the kernels that count in the workspace's head (here the persistent one: 150 tiles, at least one per SM) need it
+    # zero; fb_linear zeroes the head of a buffer it has not been given before, so a fresh allocation full of ones works
+    from ferrite_b200._lib import lib
+    rng = np.random.default_rng(11)
+    M, K, N = 32, 512, 19200
+    x, wq, tx, packed = case(rng, M, K, N, "bfp8", cuda)
+    want = x.astype(np.float64) @ wq
+    ws = torch.full((int(lib().fb_linear_workspace_bytes(M, K, N)),), 255, dtype=torch.uint8, device=cuda)
+    got = ops.linear(tx, packed, out_dtype="fp32", workspace=ws)
+    assert rel_err(to_numpy(got), want) < 2e-5
+    assert torch.equal(ops.linear(tx, packed, out_dtype="fp32", workspace=ws), got) and lib().fb_status_word() == 0
+
+
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
 @pytest.mark.parametrize("K,N,norm,epilogue", [(4096, 6144, True, "none"), (4096, 4096, False, "residual"), (4096, 28672, True, "swiglu"),
                                                (14336, 4096, False, "residual"), (100, 64, False, "none"), (64, 64, True, "none"),

@@ -29,6 +29,12 @@ def test_host_side_calls():
     assert lib.fb_packed_bytes(_lib.BFP8, 64, 64) == 4 * 1088 and lib.fb_packed_bytes(_lib.BFP4, 128, 64) == 8 * 576
     assert lib.fb_packed_bytes(_lib.BFP8, 32, 48) == 4 * 1088, "rows and columns pad to whole units"
     assert lib.fb_packed_bytes(_lib.BFP8, 32, 40) == 0, "columns come in runs of 16"
+    # fb_linear's workspace: a zeroed head of 18 KB (arrival words, row scales, counters), then partial tiles and the
+    # normalised activations; one row also leaves room for the streaming GEMV's partial sums, a slot per column group
+    # and sharing CTA
+    head = 18432
+    assert lib.fb_linear_workspace_bytes(32, 4096, 4096) >= head + 32 * 4096 * 2
+    assert lib.fb_linear_workspace_bytes(1, 4096, 128256) >= head + (128256 // 64) * 2 * 64 * 4
 
 
 def test_bad_arguments_are_refused_without_a_gpu():

@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       const uint8_t* next = rows_of(i + TEAMS);
       const int sa = ra.slot;
       mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
-      const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base;
+      const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base, slot7 = slot | (k7 << 4);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const uint32_t sc = ld_shared_u32(lut32 + top[j] * 4);
@@ -284,10 +284,11 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
         }
         load(next, j);  // this register's next bytes are on their way while the rest of the step is unpacked
         const int sl = swiglu ? ((j & 3) << 1 | j >> 2) : j;  // gate and up runs alternate: rows r and r + 16 pair up
-        const uint32_t at = slot + (sl >> 2) * 1024;
+        // chunk c of the row goes to chunk c ^ k7 of its 128-byte line: the line's address has its low seven bits clear,
+        // so (line | k7 << 4) ^ (c << 4) is that chunk's address - one operation per store
         const uint32_t c0 = (uint32_t)(sl & 3) * 2;
-        st_shared_v4(at + ((c0 ^ k7) << 4), v[0], v[1], v[2], v[3]);
-        st_shared_v4(at + (((c0 + 1) ^ k7) << 4), v[4], v[5], v[6], v[7]);
+        st_shared_v4((slot7 ^ (c0 << 4)) + (sl >> 2) * 1024, v[0], v[1], v[2], v[3]);
+        st_shared_v4((slot7 ^ ((c0 + 1) << 4)) + (sl >> 2) * 1024, v[4], v[5], v[6], v[7]);
       }
       fence_proxy_async();
       __syncwarp();
@@ -698,7 +699,7 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
       locate(i + TEAMS, next, n0, n1);
       const int sa = ra.slot;
       mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
-      const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base;
+      const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base, slot7 = slot | (k7 << 4);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const uint32_t sc = ld_shared_u32(lut32 + top[j] * 4);
@@ -714,10 +715,11 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
         }
         load(n0, n1, j);  // this register's next bytes are on their way while the rest of the step is unpacked
         const int sl = swiglu ? ((j & 3) << 1 | j >> 2) : j;  // gate and up runs alternate: rows r and r + 16 pair up
-        const uint32_t at = slot + (sl >> 2) * 1024;
+        // chunk c of the row goes to chunk c ^ k7 of its 128-byte line: the line's address has its low seven bits clear,
+        // so (line | k7 << 4) ^ (c << 4) is that chunk's address - one operation per store
         const uint32_t c0 = (uint32_t)(sl & 3) * 2;
-        st_shared_v4(at + ((c0 ^ k7) << 4), v[0], v[1], v[2], v[3]);
-        st_shared_v4(at + (((c0 + 1) ^ k7) << 4), v[4], v[5], v[6], v[7]);
+        st_shared_v4((slot7 ^ (c0 << 4)) + (sl >> 2) * 1024, v[0], v[1], v[2], v[3]);
+        st_shared_v4((slot7 ^ ((c0 + 1) << 4)) + (sl >> 2) * 1024, v[4], v[5], v[6], v[7]);
       }
       fence_proxy_async();
       __syncwarp();

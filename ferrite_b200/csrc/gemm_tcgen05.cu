@@ -247,12 +247,15 @@ __global__ void __launch_bounds__(THREADS) linear_tcgen05_kernel(const __grid_co
       if (ks * STEP_UNITS + unit >= units_total) return nullptr;
       return w + ((int64_t)ks * STEP_UNITS + unit) * UNIT;
     };
+    // this thread's bytes of a step's two column groups, from the step's first unit on: mantissas, exponents (the runs
+    // of a group lie at fixed distances behind them, so a load is a pointer and an immediate)
+    const int64_t my_q0 = g0 * KS * UNIT + ku * RUN, my_q1 = g1 * KS * UNIT + ku * RUN;
+    const int64_t my_e0 = g0 * KS * UNIT + UNIT_MANT + ku, my_e1 = g1 * KS * UNIT + UNIT_MANT + ku;
     auto load = [&](const uint8_t* rows, int j) {  // run j of the tile: group j / 4, run j % 4 of it
       const int grp = j >> 2, run = j & 3;
       if (rows != nullptr && (grp == 0 || has_g1)) {
-        const uint8_t* at = rows + (grp ? g1 : g0) * KS * UNIT;
-        q[j] = __ldg(reinterpret_cast<const RawT*>(at + (run * KSTEP + ku) * RUN));
-        top[j] = __ldg(at + UNIT_MANT + run * KSTEP + ku);
+        q[j] = __ldg(reinterpret_cast<const RawT*>(rows + (grp ? my_q1 : my_q0) + run * KSTEP * RUN));
+        top[j] = __ldg(rows + (grp ? my_e1 : my_e0) + run * KSTEP);
       } else {  // past the end of K, a column group past N, or no expert: zeros
         q[j] = RawT{};
         top[j] = 0;

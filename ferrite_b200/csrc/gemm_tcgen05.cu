@@ -676,12 +676,16 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
       u0 = g0 * KS + at.ks * STEP_UNITS + unit;
       if (g1 < G) u1 = g1 * KS + at.ks * STEP_UNITS + unit;
     };
-    auto load = [&](int u0, int u1, int j) {  // run j of the tile: group j / 4, run j % 4 of it
-      const int u = (j >> 2) ? u1 : u0, run = j & 3;
-      if (u >= 0) {
-        const uint8_t* at = W + (int64_t)u * UNIT;
-        q[j] = __ldg(reinterpret_cast<const RawT*>(at + (run * KSTEP + ku) * RUN));
-        top[j] = __ldg(at + UNIT_MANT + run * KSTEP + ku);
+    // (a step's two pointers - this thread's row in each group's unit, nullptr: zeros - are made once; a run's bytes
+    // lie at fixed distances behind them, so a load is a pointer and an immediate)
+    const uint8_t* const my_row = W + ku * RUN;
+    auto rows_at = [&](int u) -> const uint8_t* { return u >= 0 ? my_row + (int64_t)u * UNIT : nullptr; };
+    auto load = [&](const uint8_t* r0, const uint8_t* r1, int j) {  // run j of the tile: group j / 4, run j % 4 of it
+      const uint8_t* r = (j >> 2) ? r1 : r0;
+      const int run = j & 3;
+      if (r != nullptr) {
+        q[j] = __ldg(reinterpret_cast<const RawT*>(r + run * KSTEP * RUN));
+        top[j] = __ldg(r + (UNIT_MANT + run * KSTEP) - ku * (RUN - 1));
       } else {
         q[j] = RawT{};
         top[j] = 0;
@@ -692,14 +696,16 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
     {
       int u0, u1;
       locate(team, next, u0, u1);
+      const uint8_t* r0 = rows_at(u0), *r1 = rows_at(u1);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) load(u0, u1, j);
+      for (int j = 0; j < 8; ++j) load(r0, r1, j);
     }
     const uint32_t k7 = (uint32_t)(k & 7);
     for (int i = team; i < n_steps; i += TEAMS) {
       int n0, n1;
       next.advance(TEAMS, S);
       locate(i + TEAMS, next, n0, n1);
+      const uint8_t* r0 = rows_at(n0), *r1 = rows_at(n1);
       const int sa = ra.slot;
       mbar_wait(smem_u32(a_empty + sa), ra.phase ^ 1, abort_flag, WAIT_A_EMPTY);
       const uint32_t slot = sA32 + sa * A_SLOT_BYTES + row_base, slot7 = slot | (k7 << 4);
@@ -716,7 +722,7 @@ __global__ void __launch_bounds__(P_THREADS) linear_persistent_kernel(const __gr
           unpack4_word(q[j].x, sc, v);
           unpack4_word(q[j].y, sc, v + 4);
         }
-        load(n0, n1, j);  // this register's next bytes are on their way while the rest of the step is unpacked
+        load(r0, r1, j);  // this register's next bytes are on their way while the rest of the step is unpacked
         const int sl = swiglu ? ((j & 3) << 1 | j >> 2) : j;  // gate and up runs alternate: rows r and r + 16 pair up
         // chunk c of the row goes to chunk c ^ k7 of its 128-byte line: the line's address has its low seven bits clear,
         // so (line | k7 << 4) ^ (c << 4) is that chunk's address - one operation per store
